@@ -1,0 +1,445 @@
+"""CPU restatement of the Native Sparse Attention operators (TEST INFRASTRUCTURE ONLY).
+
+This module is the checker for the CUDA kernels of this repository.  It is never
+imported by the product package: only the tests, the smoke entry and the CPU
+baseline leg of the benchmark may use it.
+
+Every function restates, in plain fp32 torch on the CPU and with memory that is
+linear in the sequence length per query tile, what the reference project
+(XunhaoLai/native-sparse-attention-triton) computes.  The reference file and
+lines each function follows are cited in its docstring (paths are relative to
+the reference project root).  The restatement is pinned against the reference's
+own ``ops.torch`` implementations by the fixtures in ``tests/golden`` (made by
+``tests/golden/make_golden.py``, which imports the reference).
+
+All functions are differentiable torch code, so gradients for the backward
+parity tests come from autograd over these fp32 formulas.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Tuple
+
+import torch
+
+
+# --------------------------------------------------------------------------- #
+# sequence-length helpers
+# --------------------------------------------------------------------------- #
+def compressed_seqlens(cu_seqlens: torch.Tensor, kernel_size: int, kernel_stride: int):
+    """``(y_seqlens, y_cu_seqlens)`` after strided-window compression.
+
+    Follows native_sparse_attention/ops/triton/utils.py:25-37: a sequence of
+    length L gives ``(L - kernel_size) // kernel_stride + 1`` windows, and none
+    at all when ``L < kernel_size``.
+    """
+    seqlens = (cu_seqlens[1:] - cu_seqlens[:-1]).to(torch.int64)
+    y = torch.div(seqlens - kernel_size, kernel_stride, rounding_mode="floor") + 1
+    y = torch.where(seqlens < kernel_size, torch.zeros_like(y), y)
+    y_cu = torch.zeros(y.numel() + 1, dtype=torch.int32)
+    y_cu[1:] = torch.cumsum(y, 0).to(torch.int32)
+    return y.to(torch.int32), y_cu
+
+
+def _windows(x_seq: torch.Tensor, n_win: int, kernel_size: int, kernel_stride: int):
+    """[L, H, d] -> [n_win, kernel_size, H, d] view of the strided windows."""
+    L, H, d = x_seq.shape
+    return x_seq.as_strided(
+        (n_win, kernel_size, H, d),
+        (kernel_stride * x_seq.stride(0), x_seq.stride(0), x_seq.stride(1), x_seq.stride(2)),
+    )
+
+
+# --------------------------------------------------------------------------- #
+# compression (rows a1 / a2 of the hot-path table)
+# --------------------------------------------------------------------------- #
+def linear_compress(x, w, cu_seqlens, kernel_size, kernel_stride, pe=None):
+    """``y[m,h,:] = concat_k(x[s+m*stride+k,h,:]) @ w[h]`` plus ``concat_k(pe[h,k,:]) @ w[h]``.
+
+    Follows native_sparse_attention/ops/torch/compress_key_value.py:190-231
+    (window view -> einsum with ``w`` reshaped ``h (k d) D`` -> bias from ``pe``).
+    """
+    N, H, d = x.shape
+    y_len, y_cu = compressed_seqlens(cu_seqlens, kernel_size, kernel_stride)
+    wk = w.reshape(H, kernel_size, d, -1)
+    outs = []
+    for b in range(y_len.numel()):
+        s, m = int(cu_seqlens[b]), int(y_len[b])
+        if m == 0:
+            continue
+        win = _windows(x[s : int(cu_seqlens[b + 1])], m, kernel_size, kernel_stride)
+        outs.append(torch.einsum("nkhd,hkdD->nhD", win, wk))
+    y = torch.cat(outs, 0) if outs else x.new_zeros(0, H, w.shape[-1])
+    if pe is not None:
+        bias = torch.einsum("hD,hDd->hd", pe.reshape(H, -1), w)
+        y = y + bias.unsqueeze(0)
+    return y, y_cu
+
+
+def weightedpool_compress(x, w, cu_seqlens, kernel_size, kernel_stride, pe=None):
+    """``y[m,h,:] = sum_k w[h,k] * x[s+m*stride+k,h,:]`` plus ``sum_k w[h,k]*pe[h,k,:]``.
+
+    Follows native_sparse_attention/ops/torch/compress_key_value.py:117-153.
+    """
+    N, H, d = x.shape
+    y_len, y_cu = compressed_seqlens(cu_seqlens, kernel_size, kernel_stride)
+    outs = []
+    for b in range(y_len.numel()):
+        s, m = int(cu_seqlens[b]), int(y_len[b])
+        if m == 0:
+            continue
+        win = _windows(x[s : int(cu_seqlens[b + 1])], m, kernel_size, kernel_stride)
+        outs.append(torch.einsum("nkhd,hk->nhd", win, w))
+    y = torch.cat(outs, 0) if outs else x.new_zeros(0, H, d)
+    if pe is not None:
+        y = y + torch.einsum("hkd,hk->hd", pe, w).unsqueeze(0)
+    return y, y_cu
+
+
+def avgpool_compress(x, w, cu_seqlens, kernel_size, kernel_stride, pe=None):
+    """Mean over each window plus ``mean_k pe[h,k,:]``.
+
+    Follows native_sparse_attention/ops/torch/compress_key_value.py:52-81.
+    """
+    assert w is None, "don't need additional weight for avgpool"
+    H = x.shape[1]
+    ww = x.new_full((H, kernel_size), 1.0 / kernel_size)
+    y, y_cu = weightedpool_compress(x, ww, cu_seqlens, kernel_size, kernel_stride, None)
+    if pe is not None:
+        y = y + pe.mean(1).unsqueeze(0)
+    return y, y_cu
+
+
+# --------------------------------------------------------------------------- #
+# block scores and top-k selection
+# --------------------------------------------------------------------------- #
+def block_score_weights(kernel_size: int, kernel_stride: int, block_size: int) -> List[int]:
+    """Weights that turn compressed-key scores into selection-block scores.
+
+    ``w[o] = #{(i, j): i < kernel_size/stride, j < block_size/stride, i + j = o}``;
+    block ``b`` reads compressed key ``b*(block_size/stride) - (kernel_size/stride - 1) + o``.
+    Follows native_sparse_attention/ops/triton/compressed_attention.py:1130-1143
+    and ops/torch/compressed_attention.py:34-53.
+    """
+    a, c = kernel_size // kernel_stride, block_size // kernel_stride
+    w = [0] * (a + c - 1)
+    for i in range(a):
+        for j in range(c):
+            w[i + j] += 1
+    return w
+
+
+def block_scores_from_key_scores(score, kernel_size, kernel_stride, block_size, num_blocks):
+    """score [..., Lk] (already summed over the query heads of a KV group) -> [..., num_blocks]."""
+    a, c = kernel_size // kernel_stride, block_size // kernel_stride
+    w = block_score_weights(kernel_size, kernel_stride, block_size)
+    Lk = score.shape[-1]
+    need = (num_blocks - 1) * c + len(w)  # index after left-padding by a-1
+    padded = torch.nn.functional.pad(score, (a - 1, max(0, need - (a - 1) - Lk)))
+    out = score.new_zeros(*score.shape[:-1], num_blocks)
+    for o, wo in enumerate(w):
+        out = out + wo * padded[..., o :: c][..., :num_blocks]
+    return out
+
+
+def select_topk_blocks(block_score, q_block, topk, init_blocks, local_blocks):
+    """Top-k selection with forced blocks, ascending order, ``-1`` padding.
+
+    block_score [..., Q, num_blocks] fp32; q_block [Q] = block id of each query.
+    Blocks ``< init_blocks`` and blocks in ``(q_block - local_blocks, q_block]``
+    score ``+inf``; ``topk = min(topk, num_blocks)``; picked ids are sorted and
+    ids beyond the query's own block become ``-1``.  Follows
+    native_sparse_attention/ops/triton/compressed_attention.py:1092-1100,1289-1292.
+    """
+    nb = block_score.shape[-1]
+    b_idx = torch.arange(nb)
+    forced = (b_idx[None, :] < init_blocks) | (
+        (q_block[:, None] >= b_idx[None, :]) & (q_block[:, None] < b_idx[None, :] + local_blocks)
+    )
+    s = torch.where(forced, torch.full_like(block_score, float("inf")), block_score)
+    k = min(topk, nb)
+    idx = s.topk(k, dim=-1).indices.sort(-1).values
+    idx = torch.where(idx > q_block[:, None], torch.full_like(idx, -1), idx)
+    return idx.to(torch.int32), s
+
+
+# --------------------------------------------------------------------------- #
+# attention between queries and compressed keys (row a3)
+# --------------------------------------------------------------------------- #
+def compressed_attention(
+    q, k, v, kernel_size, kernel_stride, block_size, topk, cu_seqlens_q, cu_seqlens_k,
+    max_seqlen_q=None, max_seqlen_k=None, sm_scale=None, init_blocks=1, local_blocks=2,
+    return_scores=False,
+):
+    """Output of attention over compressed K/V, and the selected block ids.
+
+    Query at in-sequence position ``t`` sees compressed key ``i`` iff
+    ``t >= i*stride + kernel_size - 1``; rows with no visible key give 0.
+    ``score[h_kv, t, i]`` is the softmax probability summed over the query heads
+    of a KV group.  Follows
+    native_sparse_attention/ops/torch/compressed_attention.py:74-194 (mask
+    :119-133, attention :135-145, score and top-k :146-193); the number of
+    candidate blocks is ``ceil(max_seqlen_q / block_size)`` as in
+    ops/triton/compressed_attention.py:1131.
+    """
+    N, Hq, d = q.shape
+    Hkv = k.shape[1]
+    G = Hq // Hkv
+    B = cu_seqlens_q.numel() - 1
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(d)
+    seqlens_q = (cu_seqlens_q[1:] - cu_seqlens_q[:-1]).tolist()
+    if max_seqlen_q is None:
+        max_seqlen_q = max(seqlens_q)
+    num_blocks = math.ceil(max_seqlen_q / block_size)
+    outs, idxs, scores = [], [], []
+    for b in range(B):
+        qs, qe = int(cu_seqlens_q[b]), int(cu_seqlens_q[b + 1])
+        ks_, ke = int(cu_seqlens_k[b]), int(cu_seqlens_k[b + 1])
+        Lq, Lk = qe - qs, ke - ks_
+        qb = q[qs:qe].float()
+        kb = k[ks_:ke].float().repeat_interleave(G, 1)
+        vb = v[ks_:ke].float().repeat_interleave(G, 1)
+        t = torch.arange(Lq)
+        kmax = torch.arange(Lk) * kernel_stride + kernel_size - 1
+        mask = t[:, None] >= kmax[None, :]
+        logits = torch.einsum("qhd,khd->hqk", qb, kb) * sm_scale
+        logits = logits.masked_fill(~mask[None], float("-inf"))
+        p = logits.softmax(-1).nan_to_num(0)
+        outs.append(torch.einsum("hqk,khd->qhd", p, vb))
+        if topk > 0:
+            with torch.no_grad():
+                sc = p.reshape(Hkv, G, Lq, Lk).sum(1)
+                bsc = block_scores_from_key_scores(sc, kernel_size, kernel_stride, block_size, num_blocks)
+                idx, forced_sc = select_topk_blocks(bsc, t // block_size, topk, init_blocks, local_blocks)
+                idxs.append(idx)
+                scores.append(forced_sc)
+    o = torch.cat(outs, 0).to(q.dtype)
+    if topk <= 0:
+        return (o, None, None) if return_scores else (o, None)
+    topk_idx = torch.cat(idxs, 1)
+    if return_scores:
+        return o, topk_idx, torch.cat(scores, 1)
+    return o, topk_idx
+
+
+# --------------------------------------------------------------------------- #
+# attention over the selected KV blocks (row a4)
+# --------------------------------------------------------------------------- #
+def topk_sparse_attention(q, k, v, topk_idx, block_size, cu_seqlens, softmax_scale=None):
+    """Each query attends to the keys of its selected blocks, causally.
+
+    A block id is used iff ``0 <= id <= t // block_size``; inside a block key
+    position ``p`` is visible iff ``p <= t``.  Follows
+    native_sparse_attention/ops/torch/topk_sparse_attention.py:19-83 and the
+    validity rule of ops/triton/topk_sparse_attention.py:89-93,138.
+    """
+    N, Hq, d = q.shape
+    Hkv = k.shape[1]
+    G = Hq // Hkv
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(d)
+    B = cu_seqlens.numel() - 1
+    outs = []
+    for b in range(B):
+        s, e = int(cu_seqlens[b]), int(cu_seqlens[b + 1])
+        L = e - s
+        nb = math.ceil(L / block_size)
+        t = torch.arange(L)
+        idx = topk_idx[:, s:e].long()  # [Hkv, L, T]
+        valid = (idx >= 0) & (idx <= (t // block_size)[None, :, None])
+        sel = torch.zeros(Hkv, L, nb + 1, dtype=torch.bool)
+        sel.scatter_(2, torch.where(valid, idx, torch.full_like(idx, nb)), True)
+        sel = sel[..., :nb]
+        mask = sel.repeat_interleave(block_size, 2)[..., :L] & (t[None, :, None] >= t[None, None, :])
+        mask = mask.repeat_interleave(G, 0)
+        logits = torch.einsum("qhd,khd->hqk", q[s:e].float(), k[s:e].float().repeat_interleave(G, 1))
+        logits = (logits * softmax_scale).masked_fill(~mask, float("-inf"))
+        p = logits.softmax(-1).nan_to_num(0)
+        outs.append(torch.einsum("hqk,khd->qhd", p, v[s:e].float().repeat_interleave(G, 1)))
+    return torch.cat(outs, 0).to(q.dtype)
+
+
+# --------------------------------------------------------------------------- #
+# dense varlen attention (row a8)
+# --------------------------------------------------------------------------- #
+def flash_attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q=None, max_seqlen_k=None,
+                           causal=False, sm_scale=None):
+    """Dense varlen GQA attention; causal means key ``j`` visible iff ``j <= i`` (top-left aligned).
+
+    Follows native_sparse_attention/ops/triton/flash_attention.py:118-131.
+    """
+    N, Hq, d = q.shape
+    G = Hq // k.shape[1]
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(d)
+    outs = []
+    for b in range(cu_seqlens_q.numel() - 1):
+        qs, qe = int(cu_seqlens_q[b]), int(cu_seqlens_q[b + 1])
+        ks_, ke = int(cu_seqlens_k[b]), int(cu_seqlens_k[b + 1])
+        logits = torch.einsum("qhd,khd->hqk", q[qs:qe].float(), k[ks_:ke].float().repeat_interleave(G, 1)) * sm_scale
+        if causal:
+            m = torch.arange(qe - qs)[:, None] >= torch.arange(ke - ks_)[None, :]
+            logits = logits.masked_fill(~m[None], float("-inf"))
+        p = logits.softmax(-1).nan_to_num(0)
+        outs.append(torch.einsum("hqk,khd->qhd", p, v[ks_:ke].float().repeat_interleave(G, 1)))
+    return torch.cat(outs, 0).to(q.dtype)
+
+
+# --------------------------------------------------------------------------- #
+# single-token (decode) operators (rows a5 - a7)
+# --------------------------------------------------------------------------- #
+def flash_attention_decode(q, k, v, seqlens, sm_scale=None):
+    """One query token per sequence against the first ``seqlens[b]`` cache rows.
+
+    Follows native_sparse_attention/ops/triton/flash_attention_decode.py:103-128.
+    """
+    B, Hq, d = q.shape
+    G = Hq // k.shape[2]
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(d)
+    L = k.shape[1]
+    mask = torch.arange(L)[None, :] < seqlens[:, None]
+    logits = torch.einsum("bhd,bjhd->bhj", q.float(), k.float().repeat_interleave(G, 2)) * sm_scale
+    logits = logits.masked_fill(~mask[:, None, :], float("-inf"))
+    p = logits.softmax(-1).nan_to_num(0)
+    return torch.einsum("bhj,bjhd->bhd", p, v.float().repeat_interleave(G, 2)).to(q.dtype)
+
+
+def compressed_attention_decode(q, k, v, seqlens, compress_seqlens, kernel_size, kernel_stride, block_size,
+                                topk, init_blocks=1, local_blocks=2, sm_scale=None, return_scores=False):
+    """Single-token compressed attention plus block selection.
+
+    ``seqlens`` counts the current token; the query's block is
+    ``(seqlens - 1) // block_size`` and the number of candidate blocks is
+    ``ceil(max(seqlens) / block_size)``.  An empty compressed cache returns
+    zeros and an all-zero index of shape [Hkv, B, 1].  Follows
+    native_sparse_attention/ops/torch/compressed_attention_decode.py:65-153.
+    """
+    B, Hq, d = q.shape
+    _, Lc, Hkv, _ = k.shape
+    G = Hq // Hkv
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(d)
+    if Lc == 0:
+        res = (torch.zeros_like(q), torch.zeros(Hkv, B, 1, dtype=torch.int32))
+        return res + (None,) if return_scores else res
+    mask = torch.arange(Lc)[None, :] < compress_seqlens[:, None]
+    logits = torch.einsum("bhd,bjhd->bhj", q.float(), k.float().repeat_interleave(G, 2)) * sm_scale
+    logits = logits.masked_fill(~mask[:, None, :], float("-inf"))
+    p = logits.softmax(-1).nan_to_num(0)
+    o = torch.einsum("bhj,bjhd->bhd", p, v.float().repeat_interleave(G, 2)).to(q.dtype)
+    score = p.reshape(B, Hkv, G, Lc).sum(2).permute(1, 0, 2)  # [Hkv, B, Lc]
+    num_blocks = math.ceil(int(seqlens.max()) / block_size)
+    bsc = block_scores_from_key_scores(score, kernel_size, kernel_stride, block_size, num_blocks)
+    idx, forced = select_topk_blocks(bsc, (seqlens.long() - 1) // block_size, topk, init_blocks, local_blocks)
+    if return_scores:
+        return o, idx, forced
+    return o, idx
+
+
+def topk_sparse_attention_decode(q, k, v, topk_idx, block_size, seqlens, sm_scale=None):
+    """Single-token attention over the selected blocks of a dense cache.
+
+    Block id valid iff ``0 <= id <= (seqlens-1)//block_size``; key position
+    valid iff ``< seqlens[b]``.  Follows
+    native_sparse_attention/ops/triton/topk_sparse_attention_decode.py:66-122.
+    """
+    B, Hq, d = q.shape
+    _, L, Hkv, _ = k.shape
+    G = Hq // Hkv
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(d)
+    nb = math.ceil(L / block_size)
+    idx = topk_idx.long()  # [Hkv, B, T]
+    valid = (idx >= 0) & (idx <= ((seqlens.long() - 1) // block_size)[None, :, None])
+    sel = torch.zeros(Hkv, B, nb + 1, dtype=torch.bool)
+    sel.scatter_(2, torch.where(valid, idx, torch.full_like(idx, nb)), True)
+    mask = sel[..., :nb].repeat_interleave(block_size, 2)[..., :L]
+    mask = mask & (torch.arange(L)[None, None, :] < seqlens[None, :, None])
+    mask = mask.permute(1, 0, 2).repeat_interleave(G, 1)  # [B, Hq, L]
+    logits = torch.einsum("bhd,bjhd->bhj", q.float(), k.float().repeat_interleave(G, 2)) * sm_scale
+    logits = logits.masked_fill(~mask, float("-inf"))
+    p = logits.softmax(-1).nan_to_num(0)
+    return torch.einsum("bhj,bjhd->bhd", p, v.float().repeat_interleave(G, 2)).to(q.dtype)
+
+
+# --------------------------------------------------------------------------- #
+# comparators
+# --------------------------------------------------------------------------- #
+def compare_topk_idx(idx_test: torch.Tensor, idx_ref: torch.Tensor, ref_scores: torch.Tensor, tie_tol: float = 1e-3):
+    """Tie-aware equality of selected block ids.
+
+    idx_* [H, Q, T] int32 (ascending, -1 padded); ref_scores [H, Q, num_blocks]
+    are the reference's block scores with forced blocks at +inf.  A row passes
+    when the two id sets are equal, or when every id present in only one of the
+    sets has a reference score within ``tie_tol`` of the row's selection
+    threshold (the smallest selected reference score).  Returns
+    ``(num_bad_rows, num_rows_differing, num_rows)``.
+    """
+    H, Q, T = idx_ref.shape
+    nb = ref_scores.shape[-1]
+    a = torch.zeros(H, Q, nb + 1, dtype=torch.bool)
+    b = torch.zeros(H, Q, nb + 1, dtype=torch.bool)
+    a.scatter_(2, torch.where(idx_test >= 0, idx_test.long(), torch.full_like(idx_test, nb).long()), True)
+    b.scatter_(2, torch.where(idx_ref >= 0, idx_ref.long(), torch.full_like(idx_ref, nb).long()), True)
+    a, b = a[..., :nb], b[..., :nb]
+    same_count = a.sum(-1) == b.sum(-1)
+    diff = a ^ b
+    rows_diff = diff.any(-1)
+    inf = torch.full_like(ref_scores, float("inf"))
+    thr = torch.where(b, ref_scores, inf).amin(-1, keepdim=True)  # k-th best reference score
+    ok_elem = (~diff) | ((ref_scores - thr).abs() <= tie_tol)
+    bad_rows = (~ok_elem.all(-1)) | (~same_count)
+    return int(bad_rows.sum()), int(rows_diff.sum()), H * Q
+
+
+def error_stats(test: torch.Tensor, ref: torch.Tensor):
+    """(max abs error, mean abs error) in fp32."""
+    dlt = (test.float() - ref.float()).abs()
+    return float(dlt.max()) if dlt.numel() else 0.0, float(dlt.mean()) if dlt.numel() else 0.0
+
+
+# --------------------------------------------------------------------------- #
+# algorithmic work model (useful FLOPs: unmasked pairs only, 2 GEMMs forward, 5 backward)
+# --------------------------------------------------------------------------- #
+def visible_pairs_compressed(seqlens, kernel_size, kernel_stride) -> int:
+    total = 0
+    for L in seqlens:
+        M = 0 if L < kernel_size else (L - kernel_size) // kernel_stride + 1
+        t = torch.arange(L)
+        vis = torch.clamp(torch.div(t - kernel_size + 1, kernel_stride, rounding_mode="floor") + 1, min=0, max=M)
+        total += int(vis.sum())
+    return total
+
+
+def visible_pairs_selected(seqlens, block_size, topk) -> int:
+    """Pairs per KV head when every query selects min(topk, own_block+1) blocks incl. its own."""
+    total = 0
+    for L in seqlens:
+        t = torch.arange(L)
+        bq = t // block_size
+        nsel = torch.clamp(bq + 1, max=topk)
+        total += int(((nsel - 1) * block_size + t % block_size + 1).sum())
+    return total
+
+
+def useful_flops(seqlens, Hq, Hkv, d, kernel_size, kernel_stride, block_size, topk):
+    """dict of forward FLOPs per piece; backward = 2.5x (attention) or 2x (linear compression)."""
+    G = Hq // Hkv
+    p_cmp = visible_pairs_compressed(seqlens, kernel_size, kernel_stride)
+    p_sel = visible_pairs_selected(seqlens, block_size, topk)
+    M = sum(0 if L < kernel_size else (L - kernel_size) // kernel_stride + 1 for L in seqlens)
+    return {
+        "cmp_fwd": 4.0 * d * Hq * p_cmp,
+        "sel_fwd": 4.0 * d * G * p_sel * Hkv,
+        "lin_fwd": 2.0 * (2.0 * kernel_size * d * d * M * Hkv),
+    }
+
+
+def total_useful_flops(seqlens, Hq, Hkv, d, kernel_size, kernel_stride, block_size, topk, backward=True):
+    f = useful_flops(seqlens, Hq, Hkv, d, kernel_size, kernel_stride, block_size, topk)
+    fwd = f["cmp_fwd"] + f["sel_fwd"] + f["lin_fwd"]
+    if not backward:
+        return fwd
+    return fwd + 2.5 * (f["cmp_fwd"] + f["sel_fwd"]) + 2.0 * f["lin_fwd"]
