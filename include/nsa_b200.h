@@ -1,0 +1,130 @@
+/* C interface of libnsa_b200: the Native Sparse Attention hot path as sm_100a CUDA kernels.
+ *
+ * Conventions for every entry point
+ *   - all pointers are DEVICE pointers unless stated otherwise; nothing is allocated or freed
+ *     by the library (callers own every buffer, including scratch);
+ *   - strides are in ELEMENTS; the innermost (head_dim) stride is 1; token and head strides
+ *     must be multiples of 8 elements and base addresses 16-byte aligned;
+ *   - `dtype` is NSA_DTYPE_BF16 (0) or NSA_DTYPE_FP16 (1); head_dim is 64 or 128;
+ *   - `stream` is a cudaStream_t; the call is asynchronous on that stream of the CURRENT device;
+ *   - return value: 0 ok, -1 invalid argument, -2 unsupported configuration, -3 scratch too
+ *     small, 1000+e CUDA runtime error e.  Device-side anomalies (a bounded wait that gave
+ *     up, an index out of range) never hang or trap: they are OR-ed into a per-device status
+ *     word that nsa_last_device_status() returns and clears.
+ *
+ * Each declaration cites the function of the reference project
+ * (XunhaoLai/native-sparse-attention-triton, paths relative to its root) whose device work it
+ * replaces.
+ */
+#ifndef NSA_B200_H_
+#define NSA_B200_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NSA_DTYPE_BF16 0
+#define NSA_DTYPE_FP16 1
+
+/* Library version, (major << 16) | minor. */
+int nsa_version(void);
+
+/* OR of the device-side error bits raised since the last call (1 = bounded wait timed out,
+ * 2 = index out of range); synchronises `stream`.  No counterpart in the reference. */
+int nsa_last_device_status(void* stream);
+
+/* Forward of attention over selected KV blocks.
+ * Replaces _topk_sparse_attention_fwd / forward_kernel,
+ * native_sparse_attention/ops/triton/topk_sparse_attention.py:26-173,828-909.
+ *   q [total_len, num_q_heads, d], k/v [total_len, num_kv_heads, d], o like q,
+ *   topk_idx int32 [num_kv_heads, total_len, topk] (valid ids first, -1 padding),
+ *   cu_seqlens int32 [batch+1], lse fp32 [total_len, num_q_heads] (base-2, scaled logits).
+ *   strides[11] = {q_n, q_h, k_n, k_h, v_n, v_h, o_n, o_h, idx_h, idx_n, idx_k}. */
+int nsa_topk_sparse_attn_fwd(const void* q, const void* k, const void* v, const int* topk_idx,
+                             const int* cu_seqlens, void* o, float* lse, int total_len, int batch,
+                             int num_q_heads, int num_kv_heads, int head_dim, int topk, int block_size,
+                             const long long* strides, float sm_scale, int dtype, void* stream);
+
+/* Forward of dense varlen GQA attention with the strided-causal mask
+ *     query at in-sequence position t sees key i  iff  t >= i*stride + window - 1   (causal != 0)
+ * window = kernel_size, stride = kernel_stride: attention over compressed keys, replaces
+ * _compressed_attention_fwd / forward_kernel, native_sparse_attention/ops/triton/compressed_attention.py:27-158,538-615.
+ * window = stride = 1 (causal) or causal = 0 (full): replaces _flash_attention_fwd,
+ * native_sparse_attention/ops/triton/flash_attention.py:26-165,563-657.
+ *   q [total_q, Hq, d], k/v [total_k, Hkv, d], o like q, lse fp32 [total_q, Hq] (base 2);
+ *   rows without a visible key get o = 0 and lse = -inf.
+ *   strides[8] = {q_n, q_h, k_n, k_h, v_n, v_h, o_n, o_h}. */
+int nsa_varlen_attn_fwd(const void* q, const void* k, const void* v, const int* cu_seqlens_q,
+                        const int* cu_seqlens_k, void* o, float* lse, int total_q, int total_k, int batch,
+                        int max_seqlen_q, int num_q_heads, int num_kv_heads, int head_dim, int causal,
+                        int window, int stride, const long long* strides, float sm_scale, int dtype,
+                        void* stream);
+
+/* Block scores and top-k block selection for every query token, from q, the compressed keys and the
+ * forward pass's lse.  Replaces _get_attention_score + transform_score + torch.topk/sort/mask,
+ * native_sparse_attention/ops/triton/compressed_attention.py:851-1179,1245-1330.
+ *   topk_idx int32 [Hkv, total_q, min(topk, ceil(max_seqlen_q/block_size))]: ascending ids, -1 padding.
+ *   strides[7] = {q_n, q_h, k_n, k_h, idx_h, idx_n, idx_k}. */
+int nsa_compressed_attn_topk(const void* q, const void* k, const float* lse, const int* cu_seqlens_q,
+                             const int* cu_seqlens_k, int* topk_idx, int total_q, int total_k, int batch,
+                             int max_seqlen_q, int num_q_heads, int num_kv_heads, int head_dim,
+                             int kernel_size, int kernel_stride, int block_size, int topk, int init_blocks,
+                             int local_blocks, const long long* strides, float sm_scale, int dtype,
+                             void* stream);
+
+/* Linear compression forward: y[m,h,:] = concat_k(x[s+m*stride+k,h,:]) @ w[h] (+ concat_k(pe[h,k,:]) @ w[h]).
+ * Replaces LinearCompress.forward + the bias einsum,
+ * native_sparse_attention/ops/triton/linear_compress.py:26-136,309-417,497-525.
+ *   x [N, H, d] (strides x_stride_n, x_stride_h), w [H, kernel_size*d, d] contiguous, pe [H, kernel_size, d]
+ *   contiguous or NULL, y [total_y, H, d] contiguous, y_cu_seqlens int32 [batch+1],
+ *   bias_scratch [H, d] of the storage type (needed iff pe != NULL). */
+int nsa_linear_compress_fwd(const void* x, const void* w, const void* pe, const int* cu_seqlens,
+                            const int* y_cu_seqlens, void* y, void* bias_scratch, int batch, int total_y,
+                            int max_y_len, int num_heads, int head_dim, int kernel_size, int kernel_stride,
+                            long long x_stride_n, long long x_stride_h, int dtype, void* stream);
+
+/* Weighted (w [H, kernel_size]) or average (w == NULL) pooling compression forward.
+ * Replaces SlidingWindowWeightedPool.forward + the bias einsum/mean,
+ * native_sparse_attention/ops/triton/weighted_pool.py:23-85,182-239,301-363. */
+int nsa_pool_compress_fwd(const void* x, const void* w, const void* pe, const int* cu_seqlens,
+                          const int* y_cu_seqlens, void* y, void* bias_scratch, int batch, int total_y,
+                          int num_heads, int head_dim, int kernel_size, int kernel_stride,
+                          long long x_stride_n, long long x_stride_h, int dtype, void* stream);
+
+/* Number of split-KV partitions the decode kernels want for this problem (>= 1); the caller sizes
+ * the scratch buffer as batch*num_kv_heads*splits*16*(head_dim+2) floats.  No counterpart in the reference. */
+int nsa_decode_num_splits(int batch, int num_kv_heads, int max_tiles);
+
+/* Single-token attention over the first seqlens[b] rows of a dense cache.
+ * Replaces decode_kernel, native_sparse_attention/ops/triton/flash_attention_decode.py:22-217.
+ *   q [B, Hq, d], k/v [B, cache_len, Hkv, d] (strided views allowed), o [B, Hq, d].
+ *   strides[13] = {q_b, q_h, k_b, k_n, k_h, v_b, v_n, v_h, o_b, o_h, idx_h, idx_b, idx_k}. */
+int nsa_flash_attn_decode(const void* q, const void* k, const void* v, const int* seqlens, void* o,
+                          float* scratch, long long scratch_floats, int num_splits, int batch, int cache_len,
+                          int num_q_heads, int num_kv_heads, int head_dim, const long long* strides,
+                          float sm_scale, int dtype, void* stream);
+
+/* Single-token attention over the selected blocks of a dense cache.
+ * Replaces forward_kernel, native_sparse_attention/ops/triton/topk_sparse_attention_decode.py:22-237.
+ *   topk_idx int32 [Hkv, B, topk]. */
+int nsa_topk_sparse_attn_decode(const void* q, const void* k, const void* v, const int* topk_idx,
+                                const int* seqlens, void* o, float* scratch, long long scratch_floats,
+                                int num_splits, int batch, int cache_len, int num_q_heads, int num_kv_heads,
+                                int head_dim, int topk, int block_size, const long long* strides,
+                                float sm_scale, int dtype, void* stream);
+
+/* Single-token attention over the compressed cache + block scores + top-k selection in one kernel.
+ * Replaces compressed_attention_decode (about 15 ATen launches),
+ * native_sparse_attention/ops/torch/compressed_attention_decode.py:21-153.
+ *   topk_idx int32 [Hkv, B, min(topk, ceil(max_seqlen/block_size))] or NULL (output only). */
+int nsa_compressed_attn_decode(const void* q, const void* k, const void* v, const int* seqlens,
+                               const int* compress_seqlens, void* o, int* topk_idx, int batch, int cache_len,
+                               int max_seqlen, int num_q_heads, int num_kv_heads, int head_dim,
+                               int kernel_size, int kernel_stride, int block_size, int topk, int init_blocks,
+                               int local_blocks, const long long* strides, float sm_scale, int dtype,
+                               void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NSA_B200_H_ */

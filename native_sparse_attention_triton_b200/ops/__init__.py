@@ -1,0 +1,20 @@
+"""The operator namespace: same nine names as the reference's ``native_sparse_attention.ops``."""
+from .compress import avgpool_compress, linear_compress, weightedpool_compress
+from .compressed_attention import compressed_attention
+from .decode import compressed_attention_decode, flash_attention_decode, topk_sparse_attention_decode
+from .flash_attention import flash_attention_varlen
+from .topk_sparse_attention import topk_sparse_attention
+from .utils import get_compressed_seqlens
+
+__all__ = [
+    "avgpool_compress",
+    "weightedpool_compress",
+    "linear_compress",
+    "flash_attention_varlen",
+    "compressed_attention",
+    "topk_sparse_attention",
+    "flash_attention_decode",
+    "compressed_attention_decode",
+    "topk_sparse_attention_decode",
+    "get_compressed_seqlens",
+]

@@ -1,0 +1,59 @@
+"""Helpers shared by the operator wrappers: argument plumbing between torch tensors and the C ABI."""
+import math
+from typing import List, Tuple
+
+import torch
+
+from .. import _lib
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return _lib.DTYPE_BF16
+    if t.dtype == torch.float16:
+        return _lib.DTYPE_FP16
+    raise AssertionError("only bfloat16 and float16 tensors are supported")
+
+
+def stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("native_sparse_attention_triton_b200 ops run on CUDA tensors only (no CPU path)")
+
+
+def inner_contiguous(t: torch.Tensor) -> torch.Tensor:
+    """Kernels need a unit innermost stride, 16-byte aligned rows; copy only when that does not hold."""
+    ok = t.stride(-1) == 1 and t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:-1])
+    return t if ok else t.contiguous()
+
+
+def host_seqlens(cu_seqlens: torch.Tensor) -> List[int]:
+    """cu_seqlens -> python list (one device-to-host copy)."""
+    return cu_seqlens.tolist()
+
+
+def compressed_lens(cu: List[int], kernel_size: int, kernel_stride: int) -> List[int]:
+    out = []
+    for i in range(len(cu) - 1):
+        L = cu[i + 1] - cu[i]
+        out.append(0 if L < kernel_size else (L - kernel_size) // kernel_stride + 1)
+    return out
+
+
+def cumsum_tensor(lens: List[int], device) -> torch.Tensor:
+    cu = [0]
+    for x in lens:
+        cu.append(cu[-1] + x)
+    return torch.tensor(cu, dtype=torch.int32, device=device)
+
+
+def default_scale(head_dim: int) -> float:
+    return 1.0 / math.sqrt(head_dim)
