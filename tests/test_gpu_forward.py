@@ -29,9 +29,14 @@ def dev(t, dtype=torch.bfloat16):
 
 
 def close(test, ref, what, mx=MAX_TOL, mean=MEAN_TOL):
+    """max |err| <= mx * max(1, |ref|) elementwise (a 16-bit result of magnitude 4..8 carries up to 3e-2 of
+    representation error alone), mean |err| <= mean."""
     assert test.shape == ref.shape, (what, test.shape, ref.shape)
-    a, b = O.error_stats(test.float().cpu(), ref.float().cpu())
-    assert a <= mx and b <= mean, (what, a, b)
+    t, r = test.float().cpu(), ref.float().cpu()
+    err = (t - r).abs()
+    worst = float((err / r.abs().clamp(min=1.0)).max()) if err.numel() else 0.0
+    avg = float(err.mean()) if err.numel() else 0.0
+    assert worst <= mx and avg <= mean, (what, worst, avg)
 
 
 GOLDEN = ["mini_ragged", "cfg1", "g16_d128"]
