@@ -26,11 +26,22 @@ _SIGNATURES = {
                                  _I, _P],
     "nsa_linear_compress_fwd": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _L, _I, _P],
     "nsa_pool_compress_fwd": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _L, _L, _I, _P],
+    "nsa_varlen_attn_bwd": [_P] * 12 + [_L] + [_I] * 11 + [_P, _F, _I, _P],
+    "nsa_topk_sparse_attn_bwd": [_P] * 13 + [_L] + [_I] * 7 + [_P, _F, _I, _P],
+    "nsa_linear_compress_bwd": [_P] * 10 + [_I] * 8 + [_L, _L, _I, _P],
+    "nsa_pool_compress_bwd": [_P] * 10 + [_I] * 7 + [_L, _L, _I, _P],
     "nsa_decode_num_splits": [_I, _I, _I],
     "nsa_flash_attn_decode": [_P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P, _F, _I, _P],
     "nsa_topk_sparse_attn_decode": [_P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _P, _F, _I, _P],
     "nsa_compressed_attn_decode": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P,
                                    _F, _I, _P],
+}
+
+
+# functions that return a byte count (long long)
+_SIZE_QUERIES = {
+    "nsa_varlen_attn_bwd_workspace": [_I, _I, _I, _I, _I],
+    "nsa_topk_sparse_attn_bwd_workspace": [_I, _I, _I, _I, _I, _I, _I],
 }
 
 
@@ -59,12 +70,16 @@ def lib() -> ctypes.CDLL:
             fn = getattr(handle, name)  # AttributeError here means header and library disagree
             fn.argtypes = argtypes
             fn.restype = c_int
+        for name, argtypes in _SIZE_QUERIES.items():
+            fn = getattr(handle, name)
+            fn.argtypes = argtypes
+            fn.restype = c_longlong
         _lib = handle
     return _lib
 
 
 def exported_symbols():
-    return sorted(_SIGNATURES)
+    return sorted(list(_SIGNATURES) + list(_SIZE_QUERIES))
 
 
 _ERRORS = {-1: "invalid argument", -2: "unsupported configuration", -3: "scratch buffer too small",
