@@ -1,0 +1,345 @@
+#!/usr/bin/env python
+"""Benchmark of the NSA hot path: linear compression -> compressed attention (+ top-k selection) ->
+top-k sparse attention, forward and backward, on one 65536-token sequence per GPU.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...     # the reference's algorithm on the host cores (CPU oracle port)
+
+Rank 0 prints ONE JSON line.  `value` is milliseconds per forward+backward step with inputs resident in
+HBM (CUDA events, max over ranks); `e2e` is the same step driven from pinned host buffers with the
+host->device copies and the device->host read of the loss inside the timed region.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+# ----------------------------------------------------------------------------------------------------
+# workload (the configuration the headline metric is quoted on)
+# ----------------------------------------------------------------------------------------------------
+WORKLOAD = dict(tokens=65536, Hq=64, Hkv=4, d=128, ks=32, st=16, bs=64, topk=16, init_blocks=1, local_blocks=2)
+METRIC = "nsa_fwd_bwd_ms_at_64k_tokens"
+CPU_SAMPLE_TOKENS = 2048  # prefix length the CPU baseline is timed on (oracle memory is quadratic in it)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm=p["hbm_gbs"], tc_burst=p["bf16_tflops"], tc_sustained=p["bf16_tflops_sustained"], source="measured")
+    return dict(hbm=6650.0, tc_burst=1590.0, tc_sustained=1400.0, source="fallback")
+
+
+def flop_model(tokens):
+    from oracle import nsa_oracle as O
+    w = WORKLOAD
+    f = O.useful_flops([tokens], w["Hq"], w["Hkv"], w["d"], w["ks"], w["st"], w["bs"], w["topk"])
+    total = O.total_useful_flops([tokens], w["Hq"], w["Hkv"], w["d"], w["ks"], w["st"], w["bs"], w["topk"])
+    return f, total
+
+
+def make_inputs(tokens, seed, device, pin=False):
+    """Seeded synthetic tensors with the shapes and distributions of the workload (q, k, v ~ N(0,1);
+    W ~ N(0, 1/(ks*d)); pe ~ N(0, 0.02^2); upstream gradients ~ N(0,1))."""
+    w = WORKLOAD
+    g = torch.Generator().manual_seed(seed)
+    N, Hq, Hkv, d, ks = tokens, w["Hq"], w["Hkv"], w["d"], w["ks"]
+
+    def mk(*shape, scale=1.0):
+        t = (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16)
+        return t.pin_memory() if pin else t
+
+    host = dict(q=mk(N, Hq, d), k=mk(N, Hkv, d), v=mk(N, Hkv, d), wk=mk(Hkv, ks * d, d, scale=1 / math.sqrt(ks * d)),
+                wv=mk(Hkv, ks * d, d, scale=1 / math.sqrt(ks * d)), pe=mk(Hkv, ks, d, scale=0.02),
+                do1=mk(N, Hq, d), do2=mk(N, Hq, d))
+    return host
+
+
+def chain_step(ops, t, cu, max_q, max_k):
+    """One forward+backward pass of the operator chain through the public Python API; returns the loss tensor."""
+    w = WORKLOAD
+    for n in ("q", "k", "v", "wk", "wv", "pe"):
+        t[n].grad = None
+    ck, cu_k = ops.linear_compress(t["k"], t["wk"], cu, w["ks"], w["st"], t["pe"])
+    cv, _ = ops.linear_compress(t["v"], t["wv"], cu, w["ks"], w["st"], None)
+    o1, idx = ops.compressed_attention(t["q"], ck, cv, w["ks"], w["st"], w["bs"], w["topk"], cu, cu_k, max_q, max_k, None,
+                                       w["init_blocks"], w["local_blocks"])
+    o2 = ops.topk_sparse_attention(t["q"], t["k"], t["v"], idx, w["bs"], cu)
+    torch.autograd.backward([o1, o2], [t["do1"], t["do2"]])
+    return o1, o2
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples of one GPU during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-lms", "200"], stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[])
+        if self.p is None:
+            return out
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        self.f.flush()
+        rows = [r.split(", ") for r in open(self.f.name).read().strip().splitlines() if r.strip()]
+        os.unlink(self.f.name)
+        sm, reasons = [], set()
+        for r in rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                out["sm_max_mhz"] = float(r[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if val.strip().lower().startswith("active"):
+                    reasons.add(name)
+        if sm:
+            sm.sort()
+            out["sm_mhz"] = sm[len(sm) // 2]
+        out["reasons"] = sorted(reasons)
+        out["samples"] = len(sm)
+        return out
+
+
+# ----------------------------------------------------------------------------------------------------
+# CPU baseline: the reference's algorithm (CPU oracle port) on a bounded prefix of the workload
+# ----------------------------------------------------------------------------------------------------
+def cpu_chain_seconds(tokens, repeats=1):
+    from oracle import nsa_oracle as O
+    w = WORKLOAD
+    torch.set_num_threads(os.cpu_count() or 1)
+    host = make_inputs(tokens, 1234, "cpu")
+    cu = torch.tensor([0, tokens], dtype=torch.int32)
+    best = None
+    for _ in range(repeats):
+        t = {n: host[n].float().requires_grad_(n in ("q", "k", "v", "wk", "wv", "pe")) for n in host}
+        t0 = time.perf_counter()
+        ck, cu_k = O.linear_compress(t["k"], t["wk"], cu, w["ks"], w["st"], t["pe"])
+        cv, _ = O.linear_compress(t["v"], t["wv"], cu, w["ks"], w["st"], None)
+        o1, idx = O.compressed_attention(t["q"], ck, cv, w["ks"], w["st"], w["bs"], w["topk"], cu, cu_k,
+                                         init_blocks=w["init_blocks"], local_blocks=w["local_blocks"])
+        o2 = O.topk_sparse_attention(t["q"], t["k"], t["v"], idx, w["bs"], cu)
+        torch.autograd.backward([o1, o2], [t["do1"], t["do2"]])
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return best
+
+
+def cpu_baseline_record(sample_tokens, seconds):
+    _, f_full = flop_model(WORKLOAD["tokens"])
+    _, f_sample = flop_model(sample_tokens)
+    ms_full = seconds * 1e3 * f_full / f_sample
+    return dict(value=ms_full, unit="ms", cores=os.cpu_count() or 1, kind="port",
+                sample=(f"oracle port (fp32 torch on the host cores) timed on the first {sample_tokens} tokens of the workload "
+                        f"({seconds:.2f} s for fwd+bwd), scaled to 65536 tokens by the useful-FLOP ratio {f_full / f_sample:.1f}"))
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    sample = 1024
+    for _ in range(min(args.warmup, 1)):
+        cpu_chain_seconds(sample)
+    times = [cpu_chain_seconds(sample) for _ in range(max(1, args.steps))]
+    sec = sum(times) / len(times)
+    rec = cpu_baseline_record(sample, sec)
+    line = dict(impl="reference", metric=METRIC, value=rec["value"], unit="ms", n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=rec["value"], higher_is_better=False, scaling="weak", vs_baseline=None,
+                dtype="f32", data="synthetic", config=config_record(), cpu_baseline=rec,
+                e2e=dict(value=rec["value"], unit="ms", h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
+    print(json.dumps(line), flush=True)
+
+
+def config_record():
+    w = WORKLOAD
+    return dict(workload=(f"NSA operator chain fwd+bwd (linear_compress k,v -> compressed_attention + top-k -> "
+                          f"topk_sparse_attention), one sequence of {w['tokens']} tokens per GPU, {w['Hq']}q/{w['Hkv']}kv heads, "
+                          f"d={w['d']}, kernel {w['ks']}/stride {w['st']}, block {w['bs']}, topk {w['topk']}, bf16"),
+                tokens_per_gpu=w["tokens"], sharding="one independent sequence per GPU, no data-path collective",
+                l2_policy="inputs (q alone is 1.07 GB) exceed the 126 MB L2; no explicit flush")
+
+
+# kernel -> (bound, algorithmic work per launch as a function of the FLOP model); see DESIGN.md
+def kernel_work(name, f):
+    cmp_f, sel_f, lin_f = f["cmp_fwd"], f["sel_fwd"], f["lin_fwd"]
+    table = {
+        "dense_fwd": ("tensor", cmp_f),            # S and PV
+        "score_topk": ("tensor", cmp_f / 2),       # S recomputed once for the scores (selection overhead)
+        "dense_dq": ("tensor", cmp_f),             # 2 of the 5 backward GEMM units
+        "dense_dkdv": ("tensor", 1.5 * cmp_f),     # 3 of the 5 backward GEMM units
+        "sparse_fwd": ("tensor", sel_f),
+        "sparse_dq": ("tensor", sel_f),
+        "sparse_dkdv": ("tensor", 1.5 * sel_f),
+        "linear_compress_fwd": ("tensor", lin_f / 2),   # launched once per tensor (k, v)
+        "linear_dw": ("tensor", lin_f / 2),
+        "linear_dx": ("tensor", lin_f / 2),
+    }
+    return table.get(name)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=None, help="override the sequence length (parity/debug only)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.tokens:
+        WORKLOAD["tokens"] = args.tokens
+
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import native_sparse_attention_triton_b200 as pkg
+    ops = pkg.ops
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    w = WORKLOAD
+    N = w["tokens"]
+    host = make_inputs(N, 42 + rank, dev, pin=True)
+    cu = torch.tensor([0, N], dtype=torch.int32, device=dev)
+    max_q = N
+    max_k = (N - w["ks"]) // w["st"] + 1
+    grad_names = ("q", "k", "v", "wk", "wv", "pe")
+    t = {n: host[n].to(dev, non_blocking=True) for n in host}
+    for n in grad_names:
+        t[n].requires_grad_(True)
+
+    for _ in range(max(args.warmup, 3)):
+        chain_step(ops, t, cu, max_q, max_k)
+    barrier()
+    assert pkg.device_status() == 0, "device-side anomaly during warm-up"
+
+    # ---------------- timed region: K steps, inputs resident in HBM ----------------
+    sampler = ClockSampler(local) if rank == 0 else None
+    launches0 = pkg._lib.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        chain_step(ops, t, cu, max_q, max_k)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = (pkg._lib.launch_count() - launches0)
+    clocks = sampler.stop() if sampler else None
+    ms_t = torch.tensor([ms], device=dev)
+    if dist is not None:
+        dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
+    ms = float(ms_t.item())
+
+    # ---------------- per-kernel device time (CUDA events inside the library, on the launching stream) ----------------
+    pkg._lib.profile(True)
+    prof_steps = 2
+    for _ in range(prof_steps):
+        chain_step(ops, t, cu, max_q, max_k)
+    prof = pkg._lib.profile_collect()
+    pkg._lib.profile(False)
+
+    # ---------------- end to end: host buffers -> device, step, loss back to the host ----------------
+    e2e_steps = max(1, min(args.steps, 3))
+    h2d_bytes = sum(host[n].numel() * host[n].element_size() for n in host)
+    loss_host = torch.empty(1, dtype=torch.float32).pin_memory()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        with torch.no_grad():
+            for n in host:
+                t[n].copy_(host[n], non_blocking=True)
+        o1, o2 = chain_step(ops, t, cu, max_q, max_k)
+        loss = torch.dot(o1.flatten(), t["do1"].flatten()).float() + torch.dot(o2.flatten(), t["do2"].flatten()).float()
+        loss_host.copy_(loss.detach().reshape(1), non_blocking=True)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    e2e_t = torch.tensor([e2e_ms], device=dev)
+    if dist is not None:
+        dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(e2e_t.item())
+    status = pkg.device_status()
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    pk = peaks()
+    f, f_total = flop_model(N)
+    # dominant kernel and its roofline
+    per_kernel = {k: dict(launches=v[0] // prof_steps, ms_per_step=v[1] / prof_steps) for k, v in prof.items()}
+    dom = max(per_kernel, key=lambda k: per_kernel[k]["ms_per_step"]) if per_kernel else None
+    roofline = None
+    if dom:
+        work = kernel_work(dom, f)
+        n_launch = max(1, per_kernel[dom]["launches"])
+        avg_ms = per_kernel[dom]["ms_per_step"] / n_launch
+        if work:
+            achieved = work[1] / 1e12 / (avg_ms / 1e3)
+            roofline = dict(kernel=dom, bound=work[0], achieved=achieved, peak=pk["tc_sustained"], unit="TFLOP/s",
+                            frac=achieved / pk["tc_sustained"], traffic=None, launch_ms=avg_ms, peak_source=pk["source"],
+                            note="peak = sustained cuBLAS bf16 figure (kernel timed inside a long step)")
+        else:
+            roofline = dict(kernel=dom, bound="hbm", achieved=None, peak=pk["hbm"], unit="GB/s", frac=None, traffic=None,
+                            launch_ms=avg_ms, peak_source=pk["source"])
+    cpu = None
+    if not args.no_cpu_baseline:
+        sec = cpu_chain_seconds(CPU_SAMPLE_TOKENS if N >= CPU_SAMPLE_TOKENS else N)
+        cpu = cpu_baseline_record(min(N, CPU_SAMPLE_TOKENS), sec)
+    useful_tflops = f_total / 1e12 / (ms / 1e3)
+    line = dict(metric=METRIC, value=ms, unit="ms", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
+                ms_per_step=ms, higher_is_better=False, scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
+                config=config_record(), clocks=clocks,
+                e2e=dict(value=e2e_ms, unit="ms", h2d_bytes_per_step=h2d_bytes, d2h_bytes_per_step=4),
+                gpu_launches=launches, roofline=roofline, cpu_baseline=cpu,
+                tokens_per_s=world * N / (ms / 1e3), useful_tflops_per_gpu=useful_tflops,
+                frac_of_tc_peak=useful_tflops / pk["tc_sustained"], per_kernel_ms=per_kernel, device_status=status)
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

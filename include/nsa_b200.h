@@ -33,6 +33,15 @@ int nsa_version(void);
  * 2 = index out of range); synchronises `stream`.  No counterpart in the reference. */
 int nsa_last_device_status(void* stream);
 
+/* Number of kernels this library has launched in the calling process.  No counterpart in the reference. */
+long long nsa_launch_count(void);
+
+/* Per-kernel device timing: while enabled, every kernel launch is bracketed by CUDA events on its stream.
+ * nsa_profile_collect synchronises the device and writes one line "kernel launches total_ms" per kernel for
+ * the launches recorded since the previous collect (returns the bytes written).  No counterpart in the reference. */
+int nsa_profile_enable(int on);
+int nsa_profile_collect(char* buf, int buflen);
+
 /* Forward of attention over selected KV blocks.
  * Replaces _topk_sparse_attention_fwd / forward_kernel,
  * native_sparse_attention/ops/triton/topk_sparse_attention.py:26-173,828-909.
@@ -123,6 +132,60 @@ int nsa_compressed_attn_decode(const void* q, const void* k, const void* v, cons
                                int kernel_size, int kernel_stride, int block_size, int topk, int init_blocks,
                                int local_blocks, const long long* strides, float sm_scale, int dtype,
                                void* stream);
+
+/* Bytes of scratch nsa_varlen_attn_bwd needs.  No counterpart in the reference (it allocates
+ * [G, total_k, Hkv, d] per-head buffers inside _compressed_attention_bwd, compressed_attention.py:664-669). */
+long long nsa_varlen_attn_bwd_workspace(int total_q, int total_k, int num_q_heads, int num_kv_heads, int head_dim);
+
+/* Backward of nsa_varlen_attn_fwd: dq, dk, dv from (q, k, v, o, do, lse).
+ * Replaces _compressed_attention_bwd (backward_sum_o_do, backward_dkdv, backward_dq and the .sum(0) over heads),
+ * native_sparse_attention/ops/triton/compressed_attention.py:161-535,618-780, and _flash_attention_bwd,
+ * native_sparse_attention/ops/triton/flash_attention.py:168-560,660-822.
+ *   strides[16] = {q_n,q_h, k_n,k_h, v_n,v_h, o_n,o_h, do_n,do_h, dq_n,dq_h, dk_n,dk_h, dv_n,dv_h}.
+ *   dk/dv partial sums of CTAs sharing a key tile are combined with fp32 atomic adds (run-to-run
+ *   differences at fp32 rounding level, as in the reference's atomic-based kernels). */
+int nsa_varlen_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                        const float* lse, const int* cu_seqlens_q, const int* cu_seqlens_k, void* dq, void* dk,
+                        void* dv, void* workspace, long long workspace_bytes, int total_q, int total_k, int batch,
+                        int max_seqlen_q, int max_seqlen_k, int num_q_heads, int num_kv_heads, int head_dim,
+                        int causal, int window, int stride, const long long* strides, float sm_scale, int dtype,
+                        void* stream);
+
+/* Bytes of scratch nsa_topk_sparse_attn_bwd needs (fp32 dk/dv accumulators, (lse, delta) pairs, inverted index). */
+long long nsa_topk_sparse_attn_bwd_workspace(int total_len, int batch, int num_q_heads, int num_kv_heads,
+                                             int head_dim, int topk, int block_size);
+
+/* Backward of nsa_topk_sparse_attn_fwd.  Builds the block -> tokens inverted index on the device
+ * (histogram, scan, scatter; no host synchronisation) and runs the dQ and dK/dV passes.
+ * Replaces _topk_sparse_attention_bwd: backward_sum_o_do, count_query, reorder_topk_idx (argsort + 4 host
+ * syncs), backward_dkdv with its [G, N, Hkv, d] buffers and .sum(0), backward_dq,
+ * native_sparse_attention/ops/triton/topk_sparse_attention.py:176-477,480-825,912-1109.
+ *   cu_seqblocks int32 [batch+1]: prefix sum of ceil(seqlen / block_size).
+ *   strides[19] = the 16 of nsa_varlen_attn_bwd followed by {idx_h, idx_n, idx_k}. */
+int nsa_topk_sparse_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                             const float* lse, const int* topk_idx, const int* cu_seqlens,
+                             const int* cu_seqblocks, void* dq, void* dk, void* dv, void* workspace,
+                             long long workspace_bytes, int total_len, int batch, int num_q_heads,
+                             int num_kv_heads, int head_dim, int topk, int block_size, const long long* strides,
+                             float sm_scale, int dtype, void* stream);
+
+/* Backward of nsa_linear_compress_fwd: dx [N,H,d], dw [H, kernel_size*d, d], dpe [H, kernel_size, d] (iff pe).
+ * Deterministic (no floating-point atomics).  Replaces linear_compress_bwd_kernel and the autograd of the
+ * bias einsum, native_sparse_attention/ops/triton/linear_compress.py:139-306,419-494,520-524.
+ *   dbias_scratch fp32 [H, d] is needed iff pe != NULL; max_seqlen is the longest input sequence. */
+int nsa_linear_compress_bwd(const void* x, const void* w, const void* pe, const void* dy, const int* cu_seqlens,
+                            const int* y_cu_seqlens, void* dx, void* dw, void* dpe, float* dbias_scratch,
+                            int total_len, int batch, int total_y, int max_seqlen, int num_heads, int head_dim,
+                            int kernel_size, int kernel_stride, long long x_stride_n, long long x_stride_h,
+                            int dtype, void* stream);
+
+/* Backward of nsa_pool_compress_fwd: dx, dw [H, kernel_size] (iff w), dpe (iff pe).  Deterministic.
+ * Replaces sliding_pool_dxdw_kernel + dw.sum(1) and the autograd of the bias,
+ * native_sparse_attention/ops/triton/weighted_pool.py:88-179,241-298,320-324,357-362. */
+int nsa_pool_compress_bwd(const void* x, const void* w, const void* pe, const void* dy, const int* cu_seqlens,
+                          const int* y_cu_seqlens, void* dx, void* dw, void* dpe, float* dbias_scratch,
+                          int total_len, int batch, int total_y, int num_heads, int head_dim, int kernel_size,
+                          int kernel_stride, long long x_stride_n, long long x_stride_h, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

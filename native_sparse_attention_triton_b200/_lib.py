@@ -20,6 +20,8 @@ _I, _L, _F, _P = c_int, c_longlong, c_float, c_void_p
 _SIGNATURES = {
     "nsa_version": [],
     "nsa_last_device_status": [_P],
+    "nsa_profile_enable": [_I],
+    "nsa_profile_collect": [ctypes.c_char_p, _I],
     "nsa_topk_sparse_attn_fwd": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _F, _I, _P],
     "nsa_varlen_attn_fwd": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _F, _I, _P],
     "nsa_compressed_attn_topk": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _F,
@@ -42,6 +44,7 @@ _SIGNATURES = {
 _SIZE_QUERIES = {
     "nsa_varlen_attn_bwd_workspace": [_I, _I, _I, _I, _I],
     "nsa_topk_sparse_attn_bwd_workspace": [_I, _I, _I, _I, _I, _I, _I],
+    "nsa_launch_count": [],
 }
 
 
@@ -94,3 +97,23 @@ def check(rc: int, name: str) -> None:
 
 def strides_array(*values):
     return (c_longlong * len(values))(*values)
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    return int(lib().nsa_launch_count())
+
+
+def profile(enable: bool) -> None:
+    check(lib().nsa_profile_enable(1 if enable else 0), "nsa_profile_enable")
+
+
+def profile_collect():
+    """{kernel: (launches, total_ms)} for the launches recorded since the last call (synchronises)."""
+    buf = ctypes.create_string_buffer(1 << 16)
+    lib().nsa_profile_collect(buf, len(buf))
+    out = {}
+    for line in buf.value.decode().splitlines():
+        name, n, ms = line.split()
+        out[name] = (int(n), float(ms))
+    return out

@@ -699,7 +699,7 @@ static int launch_dkdv(const void* q, const void* dout, const void* k, const voi
   auto kern = dkdv_kernel<T, D, SPARSE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_rc(e);
-  kern<<<grid, 160, smem, stream>>>(tmQ, tmDO, tmK, tmV, p);
+  { LaunchScope ls_(SPARSE ? "sparse_dkdv" : "dense_dkdv", stream); kern<<<grid, 160, smem, stream>>>(tmQ, tmDO, tmK, tmV, p); }
   return cuda_rc(cudaGetLastError());
 }
 
@@ -752,7 +752,7 @@ static int run_dense_bwd(const void* q, const void* k, const void* v, const void
     if (e != cudaSuccess) return cuda_rc(e);
     const int QT = WARPS * (16 / G);
     dim3 grid((max_q + QT - 1) / QT, batch, Hkv);
-    kern<<<grid, WARPS * 32, smem, stream>>>(tmK, tmV, p);
+    { LaunchScope ls_("dense_dq", stream); kern<<<grid, WARPS * 32, smem, stream>>>(tmK, tmV, p); }
     if ((e = cudaGetLastError()) != cudaSuccess) return cuda_rc(e);
   }
   DkdvParams d;
@@ -769,8 +769,8 @@ static int run_dense_bwd(const void* q, const void* k, const void* v, const void
   int rc = launch_dkdv<T, D, false>(q, dout, k, v, ds, total_q, total_k, grid, d, stream);
   if (rc) return rc;
   const long long n4 = (long long)total_k * Hkv * (D / 4);
-  convert_rows_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(dk32, dk, total_k, Hkv, D, S[12], S[13]);
-  convert_rows_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(dv32, dv, total_k, Hkv, D, S[14], S[15]);
+  { LaunchScope ls_("convert_dk", stream); convert_rows_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(dk32, dk, total_k, Hkv, D, S[12], S[13]); }
+  { LaunchScope ls_("convert_dv", stream); convert_rows_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(dv32, dv, total_k, Hkv, D, S[14], S[15]); }
   return cuda_rc(cudaGetLastError());
 }
 
@@ -828,9 +828,9 @@ static int run_sparse_bwd(const void* q, const void* k, const void* v, const voi
   ip.capacity = (long long)Hkv * N * topk;
   ip.st = p.st;
   const long long hn = (long long)Hkv * N;
-  index_scatter_kernel<false><<<(unsigned)((hn + 255) / 256), 256, 0, stream>>>(ip);
-  index_scan_kernel<<<1, 1024, 0, stream>>>(ip);
-  index_scatter_kernel<true><<<(unsigned)((hn + 255) / 256), 256, 0, stream>>>(ip);
+  { LaunchScope ls_("index_count", stream); index_scatter_kernel<false><<<(unsigned)((hn + 255) / 256), 256, 0, stream>>>(ip); }
+  { LaunchScope ls_("index_scan", stream); index_scan_kernel<<<1, 1024, 0, stream>>>(ip); }
+  { LaunchScope ls_("index_fill", stream); index_scatter_kernel<true><<<(unsigned)((hn + 255) / 256), 256, 0, stream>>>(ip); }
   if ((e = cudaGetLastError()) != cudaSuccess) return cuda_rc(e);
   {
     constexpr int WARPS = (D == 128) ? 6 : 8;
@@ -845,7 +845,7 @@ static int run_sparse_bwd(const void* q, const void* k, const void* v, const voi
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return cuda_rc(e);
     dim3 grid((N + WARPS - 1) / WARPS, Hkv);
-    kern<<<grid, WARPS * 32, smem, stream>>>(tmK, tmV, p);
+    { LaunchScope ls_("sparse_dq", stream); kern<<<grid, WARPS * 32, smem, stream>>>(tmK, tmV, p); }
     if ((e = cudaGetLastError()) != cudaSuccess) return cuda_rc(e);
   }
   DkdvParams d;
@@ -861,8 +861,8 @@ static int run_sparse_bwd(const void* q, const void* k, const void* v, const voi
   int rc = launch_dkdv<T, D, true>(q, dout, k, v, ds, N, N, grid, d, stream);
   if (rc) return rc;
   const long long n4 = (long long)N * Hkv * (D / 4);
-  convert_rows_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(dk32, dk, N, Hkv, D, S[12], S[13]);
-  convert_rows_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(dv32, dv, N, Hkv, D, S[14], S[15]);
+  { LaunchScope ls_("convert_dk", stream); convert_rows_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(dk32, dk, N, Hkv, D, S[12], S[13]); }
+  { LaunchScope ls_("convert_dv", stream); convert_rows_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(dv32, dv, N, Hkv, D, S[14], S[15]); }
   return cuda_rc(cudaGetLastError());
 }
 

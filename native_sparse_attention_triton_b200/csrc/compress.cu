@@ -200,8 +200,8 @@ template <typename T, int D>
 static int launch_linear_fwd(LinFwdParams p, const void* pe, void* bias_scratch, int B, int max_ylen, cudaStream_t stream) {
   if (pe) {
     dim3 blk(D, 1024 / D);
-    linear_bias_kernel<T><<<p.H, blk, blk.y * D * sizeof(float), stream>>>(
-        static_cast<const T*>(pe), static_cast<const T*>(p.w), static_cast<T*>(bias_scratch), p.ks * D, D);
+    { LaunchScope ls_("linear_bias", stream); linear_bias_kernel<T><<<p.H, blk, blk.y * D * sizeof(float), stream>>>(
+        static_cast<const T*>(pe), static_cast<const T*>(p.w), static_cast<T*>(bias_scratch), p.ks * D, D); }
     p.bias = bias_scratch;
   } else {
     p.bias = nullptr;
@@ -211,22 +211,22 @@ static int launch_linear_fwd(LinFwdParams p, const void* pe, void* bias_scratch,
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_rc(e);
   dim3 grid((max_ylen + 63) / 64, B, p.H);
-  kern<<<grid, 128, smem, stream>>>(p);
+  { LaunchScope ls_("linear_compress_fwd", stream); kern<<<grid, 128, smem, stream>>>(p); }
   return cuda_rc(cudaGetLastError());
 }
 
 template <typename T, int D>
 static int launch_pool_fwd(PoolFwdParams p, const void* pe, void* bias_scratch, cudaStream_t stream) {
   if (pe) {
-    pool_bias_kernel<T><<<p.H, D, 0, stream>>>(static_cast<const T*>(pe), static_cast<const T*>(p.w),
-                                                static_cast<T*>(bias_scratch), p.ks, D);
+    { LaunchScope ls_("pool_bias", stream); pool_bias_kernel<T><<<p.H, D, 0, stream>>>(static_cast<const T*>(pe), static_cast<const T*>(p.w),
+                                                static_cast<T*>(bias_scratch), p.ks, D); }
     p.bias = bias_scratch;
   } else {
     p.bias = nullptr;
   }
   const long long total = (long long)p.M * p.H * (D / 8);
   const int blocks = (int)((total + 255) / 256);
-  pool_fwd_kernel<T><<<blocks, 256, 0, stream>>>(p);
+  { LaunchScope ls_("pool_compress_fwd", stream); pool_fwd_kernel<T><<<blocks, 256, 0, stream>>>(p); }
   return cuda_rc(cudaGetLastError());
 }
 

@@ -302,18 +302,18 @@ template <typename T, int D>
 static int run_linear_bwd(LinBwdParams p, void* dpe, float* dbias, int total_y, int max_len, cudaStream_t stream) {
   if (p.pe) {
     dim3 blk(D, 1024 / D);
-    colsum_kernel<T><<<p.H, blk, blk.y * D * sizeof(float), stream>>>(static_cast<const T*>(p.dy), dbias, total_y, p.H, D);
+    { LaunchScope ls_("colsum", stream); colsum_kernel<T><<<p.H, blk, blk.y * D * sizeof(float), stream>>>(static_cast<const T*>(p.dy), dbias, total_y, p.H, D); }
     p.dbias = dbias;
     const long long hr = (long long)p.H * p.ks * D;
-    linear_dpe_kernel<T><<<(unsigned)((hr + 255) / 256), 256, 0, stream>>>(dbias, static_cast<const T*>(p.w),
-                                                                          static_cast<T*>(dpe), p.H, p.ks * D, D);
+    { LaunchScope ls_("linear_dpe", stream); linear_dpe_kernel<T><<<(unsigned)((hr + 255) / 256), 256, 0, stream>>>(dbias, static_cast<const T*>(p.w),
+                                                                          static_cast<T*>(dpe), p.H, p.ks * D, D); }
   }
   {
     const size_t smem = 1024 + 4 * 64 * D * 2;
     auto kern = linear_dw_kernel<T, D>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return cuda_rc(e);
-    kern<<<dim3(p.ks, p.H), D * 2, smem, stream>>>(p);
+    { LaunchScope ls_("linear_dw", stream); kern<<<dim3(p.ks, p.H), D * 2, smem, stream>>>(p); }
   }
   {
     const size_t smem = 1024 + D * D * 2;
@@ -321,7 +321,7 @@ static int run_linear_bwd(LinBwdParams p, void* dpe, float* dbias, int total_y, 
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return cuda_rc(e);
     const int chunks = (max_len + p.stride - 1) / p.stride;
-    kern<<<dim3((chunks + 63) / 64, p.stride, p.B * p.H), 128, smem, stream>>>(p);
+    { LaunchScope ls_("linear_dx", stream); kern<<<dim3((chunks + 63) / 64, p.stride, p.B * p.H), 128, smem, stream>>>(p); }
   }
   return cuda_rc(cudaGetLastError());
 }
@@ -330,12 +330,12 @@ template <typename T, int D>
 static int run_pool_bwd(PoolBwdParams p, float* dbias, int total_y, cudaStream_t stream) {
   if (p.pe) {
     dim3 blk(D, 1024 / D);
-    colsum_kernel<T><<<p.H, blk, blk.y * D * sizeof(float), stream>>>(static_cast<const T*>(p.dy), dbias, total_y, p.H, D);
+    { LaunchScope ls_("colsum", stream); colsum_kernel<T><<<p.H, blk, blk.y * D * sizeof(float), stream>>>(static_cast<const T*>(p.dy), dbias, total_y, p.H, D); }
     p.dbias = dbias;
   }
   const long long total = (long long)p.N * p.H * (D / 8);
-  pool_dx_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(p);
-  if (p.dw || p.dpe) pool_dw_kernel<T><<<dim3(p.H, p.ks), 256, 0, stream>>>(p);
+  { LaunchScope ls_("pool_dx", stream); pool_dx_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(p); }
+  if (p.dw || p.dpe) { LaunchScope ls_("pool_dw", stream); pool_dw_kernel<T><<<dim3(p.H, p.ks), 256, 0, stream>>>(p); }
   return cuda_rc(cudaGetLastError());
 }
 

@@ -185,9 +185,9 @@ static int launch_decode(const void* k, const void* v, const long long* kv_strid
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_rc(e);
   const int tasks = p.B * p.Hkv * p.S;
-  kern<<<(tasks + WARPS - 1) / WARPS, WARPS * 32, smem, stream>>>(tmK, tmV, p);
+  { LaunchScope ls_("decode_attn", stream); kern<<<(tasks + WARPS - 1) / WARPS, WARPS * 32, smem, stream>>>(tmK, tmV, p); }
   if (p.S > 1)
-    decode_combine_kernel<T><<<p.B * p.Hkv, 256, 0, stream>>>(p.part_o, p.part_ml, p.o, p.o_sb, p.o_sh, p.Hkv, p.G, p.S, D);
+    { LaunchScope ls_("decode_combine", stream); decode_combine_kernel<T><<<p.B * p.Hkv, 256, 0, stream>>>(p.part_o, p.part_ml, p.o, p.o_sb, p.o_sh, p.Hkv, p.G, p.S, D); }
   return cuda_rc(cudaGetLastError());
 }
 
@@ -382,7 +382,7 @@ static int launch_cmp_decode(const void* k, const void* v, const long long* kv_s
   auto kern = cmp_decode_kernel<T, D>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_rc(e);
-  kern<<<dim3(p.B, p.Hkv), WARPS * 32, smem, stream>>>(tmK, tmV, p);
+  { LaunchScope ls_("cmp_decode", stream); kern<<<dim3(p.B, p.Hkv), WARPS * 32, smem, stream>>>(tmK, tmV, p); }
   return cuda_rc(cudaGetLastError());
 }
 

@@ -171,7 +171,7 @@ static int launch_dense_fwd(const void* k, const void* v, long long k_sn, long l
   if (e != cudaSuccess) return cuda_rc(e);
   const int QT = WARPS * (16 / p.G);
   dim3 grid((max_seqlen_q + QT - 1) / QT, p.B, p.Hkv);
-  kern<<<grid, WARPS * 32, smem, stream>>>(tmK, tmV, p);
+  { LaunchScope ls_("dense_fwd", stream); kern<<<grid, WARPS * 32, smem, stream>>>(tmK, tmV, p); }
   return cuda_rc(cudaGetLastError());
 }
 

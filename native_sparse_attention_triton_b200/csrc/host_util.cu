@@ -1,7 +1,13 @@
 #include "host_util.h"
 
 #include <cudaTypedefs.h>
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <map>
 #include <mutex>
+#include <string>
+#include <vector>
 
 namespace nsa {
 
@@ -75,6 +81,74 @@ int read_status(cudaStream_t stream) {
 }
 
 }  // namespace nsa
+
+namespace nsa {
+static std::atomic<long long> g_launches{0};
+static bool g_prof_on = false;
+struct Pending { std::string tag; cudaEvent_t a, b; };
+static std::vector<Pending> g_pending;
+static std::vector<cudaEvent_t> g_free_events;
+static std::mutex g_prof_mu;
+
+static cudaEvent_t get_event() {
+  if (!g_free_events.empty()) { cudaEvent_t e = g_free_events.back(); g_free_events.pop_back(); return e; }
+  cudaEvent_t e = nullptr;
+  cudaEventCreate(&e);
+  return e;
+}
+
+void launch_begin(const char* tag, cudaStream_t stream) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (!g_prof_on) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  Pending pd{tag, get_event(), get_event()};
+  cudaEventRecord(pd.a, stream);
+  g_pending.push_back(pd);
+}
+
+void launch_end(cudaStream_t stream) {
+  if (!g_prof_on) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  if (!g_pending.empty()) cudaEventRecord(g_pending.back().b, stream);
+}
+}  // namespace nsa
+
+extern "C" long long nsa_launch_count(void) { return nsa::g_launches.load(); }
+
+extern "C" int nsa_profile_enable(int on) {
+  std::lock_guard<std::mutex> lk(nsa::g_prof_mu);
+  nsa::g_prof_on = on != 0;
+  return 0;
+}
+
+// Writes one line per kernel tag, "tag launches total_ms\n", for every launch recorded since the last call;
+// synchronises the device.  Returns the number of bytes written (0 when nothing was recorded).
+extern "C" int nsa_profile_collect(char* buf, int buflen) {
+  using namespace nsa;
+  cudaDeviceSynchronize();
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  std::map<std::string, std::pair<long long, double>> acc;
+  std::vector<std::string> order;
+  for (auto& pd : g_pending) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, pd.a, pd.b) == cudaSuccess) {
+      if (!acc.count(pd.tag)) order.push_back(pd.tag);
+      acc[pd.tag].first += 1;
+      acc[pd.tag].second += ms;
+    }
+    g_free_events.push_back(pd.a);
+    g_free_events.push_back(pd.b);
+  }
+  g_pending.clear();
+  int n = 0;
+  for (auto& t : order) {
+    char line[160];
+    const int len = snprintf(line, sizeof line, "%s %lld %.6f\n", t.c_str(), acc[t].first, acc[t].second);
+    if (buf && n + len < buflen) { memcpy(buf + n, line, len); n += len; }
+  }
+  if (buf && n < buflen) buf[n] = 0;
+  return n;
+}
 
 extern "C" int nsa_version(void) { return (0 << 16) | 1; }
 

@@ -32,6 +32,17 @@ int* status_word();
 // read-and-clear; returns the OR of error bits raised by kernels since the last call
 int read_status(cudaStream_t stream);
 
+// Launch accounting.  Every kernel launch of the library sits inside a LaunchScope: it always bumps a
+// process-wide launch counter and, when profiling is enabled (nsa_profile_enable), brackets the launch
+// with CUDA events on the launching stream so that per-kernel device time can be read back.
+void launch_begin(const char* tag, cudaStream_t stream);
+void launch_end(cudaStream_t stream);
+struct LaunchScope {
+  cudaStream_t s;
+  LaunchScope(const char* tag, cudaStream_t stream) : s(stream) { launch_begin(tag, stream); }
+  ~LaunchScope() { launch_end(s); }
+};
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace nsa

@@ -207,7 +207,7 @@ static int launch_score_topk(const void* k, long long k_sn, long long k_sh, int 
   if (e != cudaSuccess) return cuda_rc(e);
   const int QT = nwarps * QPW;
   dim3 grid((max_seqlen_q + QT - 1) / QT, p.B, p.Hkv);
-  kern<<<grid, nwarps * 32, smem, stream>>>(tmK, p);
+  { LaunchScope ls_("score_topk", stream); kern<<<grid, nwarps * 32, smem, stream>>>(tmK, p); }
   return cuda_rc(cudaGetLastError());
 }
 

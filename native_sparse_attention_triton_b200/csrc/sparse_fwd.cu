@@ -146,7 +146,7 @@ static int launch_sparse_fwd(const void* k, const void* v, long long k_sn, long 
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_rc(e);
   dim3 grid((p.N + WARPS - 1) / WARPS, p.Hkv);
-  kern<<<grid, WARPS * 32, smem, stream>>>(tmK, tmV, p);
+  { LaunchScope ls_("sparse_fwd", stream); kern<<<grid, WARPS * 32, smem, stream>>>(tmK, tmV, p); }
   return cuda_rc(cudaGetLastError());
 }
 
