@@ -1,0 +1,75 @@
+"""Drop-in installation: make the reference project's own modules bind to these operators.
+
+The reference's callers import the operators by name at import time:
+  native_sparse_attention/module/native_sparse_attention.py:16-22 (and the dict COMPRESS_TYPE_TO_FUNC, :28-32)
+  native_sparse_attention/infer/inference_func.py:17-24
+  native_sparse_attention/module/self_attention.py:19
+  native_sparse_attention/module/kv_cache.py:18 (get_compressed_seqlens from ops.triton.utils)
+
+`install()` registers this package's operator namespace in ``sys.modules`` under the names
+``native_sparse_attention.ops``, ``native_sparse_attention.ops.triton`` and
+``native_sparse_attention.ops.triton.utils`` so that a later ``import native_sparse_attention.module`` binds to
+the CUDA kernels of libnsa_b200.so and the reference's Triton sources are never imported.  When the reference
+has already been imported, the binding sites listed above are rewritten in place as well.
+"""
+import sys
+import types
+
+from . import ops as _ops
+
+_OP_NAMES = [
+    "avgpool_compress", "weightedpool_compress", "linear_compress", "flash_attention_varlen", "compressed_attention",
+    "topk_sparse_attention", "flash_attention_decode", "compressed_attention_decode", "topk_sparse_attention_decode",
+]
+_PKG = "native_sparse_attention"
+
+
+def _module(name, is_pkg, **attrs):
+    m = types.ModuleType(name)
+    m.__dict__.update(attrs)
+    if is_pkg:
+        m.__path__ = []  # a package without files: submodules must be pre-registered
+    m.__nsa_b200_shim__ = True
+    return m
+
+
+def install(patch_loaded: bool = True):
+    """Route ``native_sparse_attention.ops`` (and ``.ops.triton.utils``) to this package.  Returns the ops module."""
+    fns = {n: getattr(_ops, n) for n in _OP_NAMES}
+    ops_mod = _module(f"{_PKG}.ops", True, __all__=list(_OP_NAMES), **fns)
+    triton_mod = _module(f"{_PKG}.ops.triton", True)
+    utils_mod = _module(f"{_PKG}.ops.triton.utils", False, get_compressed_seqlens=_ops.get_compressed_seqlens,
+                        is_hopper_gpu=lambda: False)
+    ops_mod.triton = triton_mod
+    triton_mod.utils = utils_mod
+    sys.modules[f"{_PKG}.ops"] = ops_mod
+    sys.modules[f"{_PKG}.ops.triton"] = triton_mod
+    sys.modules[f"{_PKG}.ops.triton.utils"] = utils_mod
+    parent = sys.modules.get(_PKG)
+    if parent is not None:
+        parent.ops = ops_mod
+    if patch_loaded:
+        _patch_loaded_modules(fns)
+    return ops_mod
+
+
+def _patch_loaded_modules(fns):
+    """Rewrite names that already-imported reference modules captured."""
+    for name, mod in list(sys.modules.items()):
+        if mod is None or not name.startswith(_PKG + ".") or name.startswith(_PKG + ".ops"):
+            continue
+        for fn_name, fn in fns.items():
+            if hasattr(mod, fn_name):
+                setattr(mod, fn_name, fn)
+        if hasattr(mod, "get_compressed_seqlens"):
+            mod.get_compressed_seqlens = _ops.get_compressed_seqlens
+        table = getattr(mod, "COMPRESS_TYPE_TO_FUNC", None)
+        if isinstance(table, dict):
+            for key, fn_name in (("avgpool", "avgpool_compress"), ("weightedpool", "weightedpool_compress"),
+                                 ("linear", "linear_compress")):
+                if key in table:
+                    table[key] = fns[fn_name]
+
+
+def installed() -> bool:
+    return getattr(sys.modules.get(f"{_PKG}.ops"), "__nsa_b200_shim__", False)
