@@ -113,6 +113,24 @@ int nsa_flash_attn_decode(const void* q, const void* k, const void* v, const int
                           int num_q_heads, int num_kv_heads, int head_dim, const long long* strides,
                           float sm_scale, int dtype, void* stream);
 
+/* nsa_flash_attn_decode for callers that are not allowed to allocate device memory (a server that gave its
+ * whole memory budget to its own pool at start-up, a loop that must avoid the device synchronisation an
+ * allocation can imply).  It has no counterpart in the reference.  The split-KV scratch is an 8 MiB array
+ * inside the library's device image (held by every GPU that loads the library, until the process exits);
+ * the caller passes inputs and the output only.  No cudaMalloc/cudaFree or allocating routine is called.
+ *   num_splits: 0 = library default (nsa_decode_num_splits); the call needs
+ *       batch*num_kv_heads*splits*16*(head_dim+2) floats and returns -3 when that exceeds
+ *       nsa_flash_attn_decode_static_capacity() floats -- ask for fewer splits (1 needs none).
+ *   The first call on a device looks up the array's device address (cudaGetSymbolAddress, once per device,
+ *   with that device current): make that first call before any stream capture.
+ *   All calls on a device share the one array and it keeps the previous call's contents; nothing has to be
+ *   cleared (each call writes every slot it later reads), but two calls that overlap on the GPU (different
+ *   streams, or host threads) race on it: serialise them. */
+long long nsa_flash_attn_decode_static_capacity(void);
+int nsa_flash_attn_decode_static(const void* q, const void* k, const void* v, const int* seqlens, void* o,
+                                 int num_splits, int batch, int cache_len, int num_q_heads, int num_kv_heads,
+                                 int head_dim, const long long* strides, float sm_scale, int dtype, void* stream);
+
 /* Single-token attention over the selected blocks of a dense cache.
  * Replaces forward_kernel, native_sparse_attention/ops/triton/topk_sparse_attention_decode.py:22-237.
  *   topk_idx int32 [Hkv, B, topk]. */

@@ -34,6 +34,7 @@ _SIGNATURES = {
     "nsa_pool_compress_bwd": [_P] * 10 + [_I] * 7 + [_L, _L, _I, _P],
     "nsa_decode_num_splits": [_I, _I, _I],
     "nsa_flash_attn_decode": [_P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P, _F, _I, _P],
+    "nsa_flash_attn_decode_static": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _F, _I, _P],
     "nsa_topk_sparse_attn_decode": [_P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _P, _F, _I, _P],
     "nsa_compressed_attn_decode": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P,
                                    _F, _I, _P],
@@ -45,6 +46,7 @@ _SIZE_QUERIES = {
     "nsa_varlen_attn_bwd_workspace": [_I, _I, _I, _I, _I],
     "nsa_topk_sparse_attn_bwd_workspace": [_I, _I, _I, _I, _I, _I, _I],
     "nsa_launch_count": [],
+    "nsa_flash_attn_decode_static_capacity": [],
 }
 
 

@@ -494,3 +494,61 @@ extern "C" int nsa_compressed_attn_decode(const void* q, const void* k, const vo
   const long long kvs[6] = {strides[2], strides[3], strides[4], strides[5], strides[6], strides[7]};
   return NSA_DISPATCH_T_D(dtype, head_dim, launch_cmp_decode, k, v, kvs, cache_len, p, static_cast<cudaStream_t>(stream));
 }
+
+// ------------------------------------------------------------------------------------------------
+// Flash decode for callers that cannot allocate device memory.
+//
+// Some hosts of this library may not call cudaMalloc at all once they are running: a serving
+// process that handed its whole memory budget to its own pool at start-up (any later allocation
+// fails or fragments it), or a control loop that must not hit the implicit device synchronisation
+// an allocation can cause.  The regular entry point makes such a caller provide the split-KV
+// scratch; this variant keeps that scratch in the array below, which lives in the library's device
+// image: every GPU that loads the library holds these 8 MiB until the process exits.
+// ------------------------------------------------------------------------------------------------
+namespace nsa {
+
+constexpr long long kStaticScratchFloats = 2ll * 1024 * 1024;  // 8 MiB
+static __device__ __align__(256) float g_decode_scratch[kStaticScratchFloats];
+
+// Device address of g_decode_scratch on the current device.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel can use; the address comes from cudaGetSymbolAddress,
+// asked once per device with that device current.
+static float* g_decode_scratch_ptr[64] = {};
+
+static int static_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_rc(e);
+  if (dev < 0 || dev >= 64) return kUnsupported;
+  if (!g_decode_scratch_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_decode_scratch);
+    if (e != cudaSuccess) return cuda_rc(e);
+    g_decode_scratch_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_decode_scratch_ptr[dev];
+  return kOk;
+}
+
+}  // namespace nsa
+
+extern "C" long long nsa_flash_attn_decode_static_capacity(void) { return nsa::kStaticScratchFloats; }
+
+extern "C" int nsa_flash_attn_decode_static(const void* q, const void* k, const void* v, const int* seqlens, void* o,
+                                            int num_splits, int batch, int cache_len, int num_q_heads, int num_kv_heads,
+                                            int head_dim, const long long* strides, float sm_scale, int dtype,
+                                            void* stream) {
+  using namespace nsa;
+  if (batch <= 0 || cache_len <= 0 || num_kv_heads <= 0 || head_dim <= 0) return kInvalid;
+  const int max_tiles = (cache_len + kKeyTile - 1) / kKeyTile;
+  int splits = num_splits > 0 ? num_splits : nsa_decode_num_splits(batch, num_kv_heads, max_tiles);
+  if (splits > max_tiles) splits = max_tiles;
+  const long long need = splits > 1 ? (long long)batch * num_kv_heads * splits * 16 * (head_dim + 2) : 0;
+  if (need > kStaticScratchFloats) return kWorkspace;  // the problem does not fit the built-in scratch: use fewer splits
+  float* scratch = nullptr;
+  const int rc = static_scratch(&scratch);
+  if (rc) return rc;
+  // Every partial slot the combine step reads is written by this same call, so nothing has to be cleared.
+  return nsa_flash_attn_decode(q, k, v, seqlens, o, scratch, kStaticScratchFloats, splits, batch, cache_len, num_q_heads,
+                               num_kv_heads, head_dim, strides, sm_scale, dtype, stream);
+}
