@@ -6,6 +6,8 @@
 // A CTA owns 128 rows = (128/G query tokens) x (G query heads of one KV head); K/V tiles of 64
 // keys stream through a TMA ring shared by the 8 warps, each warp keeps its 16 rows' Q
 // fragments, running max/sum and the fp32 output accumulator in registers.
+#include <cstdlib>
+
 #include "attn_tile.cuh"
 #include "dispatch.h"
 #include "host_util.h"
@@ -175,6 +177,17 @@ static int launch_dense_fwd(const void* k, const void* v, long long k_sn, long l
   return cuda_rc(cudaGetLastError());
 }
 
+// tcgen05 implementation (dense_fwd_tc.cu)
+int varlen_attn_fwd_tc(const void* q, const void* k, const void* v, const int* cu_q, const int* cu_k, void* o, float* lse,
+                       int total_q, int total_k, int batch, int max_seqlen_q, int Hq, int Hkv, int head_dim, int causal,
+                       int window, int stride, const long long* strides, float sm_scale, int dtype, cudaStream_t stream);
+
+// The mma.sync kernel of this file stays selectable (environment variable NSA_B200_LEGACY_MMA=1) for A/B measurements.
+static bool use_legacy_mma() {
+  static const bool v = [] { const char* e = getenv("NSA_B200_LEGACY_MMA"); return e && e[0] == '1'; }();
+  return v;
+}
+
 }  // namespace nsa
 
 extern "C" int nsa_varlen_attn_fwd(const void* q, const void* k, const void* v, const int* cu_seqlens_q,
@@ -202,6 +215,10 @@ extern "C" int nsa_varlen_attn_fwd(const void* q, const void* k, const void* v, 
   p.scale2 = sm_scale * kLog2e;
   p.st.word = status_word();
   if ((p.q_sn | p.q_sh | p.o_sn | p.o_sh) % 8 || !aligned16(q) || !aligned16(o)) return kInvalid;
+  if (!use_legacy_mma())
+    return varlen_attn_fwd_tc(q, k, v, cu_seqlens_q, cu_seqlens_k, o, lse, total_q, total_k, batch, max_seqlen_q, num_q_heads,
+                              num_kv_heads, head_dim, causal, window, stride, strides, sm_scale, dtype,
+                              static_cast<cudaStream_t>(stream));
   return NSA_DISPATCH_T_D(dtype, head_dim, launch_dense_fwd, k, v, strides[2], strides[3], strides[4], strides[5],
                           total_k, max_seqlen_q, p, static_cast<cudaStream_t>(stream));
 }

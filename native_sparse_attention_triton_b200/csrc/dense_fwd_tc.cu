@@ -1,0 +1,312 @@
+// Forward of dense varlen GQA attention with the strided-causal mask on the 5th-generation tensor
+// cores (tcgen05.mma, accumulators in tensor memory).
+//
+// CTA = 128 rows = (128/G query tokens) x (G query heads of one KV head), key tiles of 128.
+//   warp 4      : TMA producer (Q once, then K and V tiles through a 2-stage ring)
+//   warp 5      : allocates TMEM; one elected thread issues S = Q K^T (SMEM x SMEM -> TMEM) and
+//                 O += P V (P from SMEM, V read MN-major) and commits to mbarriers
+//   warps 0..3  : softmax.  Thread r owns row r (TMEM lane r): it reads its 128 logits with
+//                 tcgen05.ld, keeps a lazily-updated reference maximum (O and l are rescaled only
+//                 when the row maximum grows by more than 2^8), writes P as 16-bit into the
+//                 128B-swizzled SMEM tile the P V instruction reads, and finally normalises O.
+// S is double-buffered in TMEM so that Q K^T of tile i+1 overlaps the softmax of tile i.
+// TMEM columns: [0,128) S0, [128,256) S1, [256,256+D) O.
+#include "attn_tile.cuh"
+#include "dispatch.h"
+#include "host_util.h"
+#include "nsa_b200.h"
+#include "tc5.cuh"
+
+namespace nsa {
+
+struct DenseFwdTcParams {
+  void* o;
+  float* lse;  // [Nq, Hq]
+  const int* cu_q;
+  const int* cu_k;
+  long long o_sn, o_sh;
+  int B, Hq, Hkv, G, logG;
+  int window, stride, causal;
+  float scale2;
+  Status st;
+};
+
+__device__ __forceinline__ int visible_keys_tc(int t, int Lk, int window, int stride, int causal) {
+  if (!causal) return Lk;
+  if (t < window - 1) return 0;
+  return min(Lk, (t - window + 1) / stride + 1);
+}
+
+constexpr int kTcKeyTile = 128;
+constexpr int kTcStages = 2;
+
+template <typename T, int D>
+__global__ void __launch_bounds__(192, 1)
+dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, DenseFwdTcParams p) {
+  constexpr int PANELS = D / 64;
+  constexpr int PANEL_BYTES = 128 * 128;            // 128 rows x 128 B
+  constexpr int Q_BYTES = 128 * D * 2;
+  constexpr int KV_BYTES = kTcKeyTile * D * 2;      // one K or V tile
+  constexpr int P_BYTES = 128 * kTcKeyTile * 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_sm = smem;
+  uint8_t* k_sm = q_sm + Q_BYTES;
+  uint8_t* v_sm = k_sm + kTcStages * KV_BYTES;
+  uint8_t* p_sm = v_sm + kTcStages * KV_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_sm + P_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;
+  uint64_t* v_full = k_full + kTcStages;
+  uint64_t* kv_empty = v_full + kTcStages;
+  uint64_t* s_full = kv_empty + kTcStages;
+  uint64_t* s_empty = s_full + 2;
+  uint64_t* p_full = s_empty + 2;
+  uint64_t* pv_done = p_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.y, h = blockIdx.z;
+  const int qs = __ldg(p.cu_q + b), Lq = __ldg(p.cu_q + b + 1) - qs;
+  const int ksq = __ldg(p.cu_k + b), Lk = __ldg(p.cu_k + b + 1) - ksq;
+  const int QT = 128 >> p.logG;  // tokens per CTA
+  const int qt = gridDim.x - 1 - blockIdx.x;
+  const int q0 = qt * QT;
+  if (q0 >= Lq) return;
+  const int t_hi = min(q0 + QT, Lq) - 1;
+  const int ntiles = (visible_keys_tc(t_hi, Lk, p.window, p.stride, p.causal) + kTcKeyTile - 1) / kTcKeyTile;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < kTcStages; ++s) {
+      mbar_init(k_full + s, 1);
+      mbar_init(v_full + s, 1);
+      mbar_init(kv_empty + s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(s_full + s, 1);
+      mbar_init(s_empty + s, 4);
+    }
+    mbar_init(p_full, 4);
+    mbar_init(pv_done, 1);
+    fence_barrier_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  if (warp == 4) {
+    // ===================== TMA producer =====================
+    if (lane == 0 && ntiles > 0) {
+      mbar_expect_tx(q_full, Q_BYTES);
+#pragma unroll
+      for (int pn = 0; pn < PANELS; ++pn) tma_load_3d(q_sm + pn * PANEL_BYTES, &tmQ, q_full, pn * 64, h * p.G, qs + q0);
+      for (int i = 0; i < ntiles; ++i) {
+        const int s = i % kTcStages;
+        if (i >= kTcStages) mbar_wait(kv_empty + s, ((i / kTcStages) - 1) & 1, p.st);
+        mbar_expect_tx(k_full + s, KV_BYTES);
+#pragma unroll
+        for (int pn = 0; pn < PANELS; ++pn)
+          tma_load_3d(k_sm + s * KV_BYTES + pn * PANEL_BYTES, &tmK, k_full + s, pn * 64, h, ksq + i * kTcKeyTile);
+        mbar_expect_tx(v_full + s, KV_BYTES);
+#pragma unroll
+        for (int pn = 0; pn < PANELS; ++pn)
+          tma_load_3d(v_sm + s * KV_BYTES + pn * PANEL_BYTES, &tmV, v_full + s, pn * 64, h, ksq + i * kTcKeyTile);
+      }
+    }
+  } else if (warp == 5) {
+    // ===================== MMA issuer =====================
+    if (lane == 0 && ntiles > 0) {
+      const uint32_t idesc_qk = umma_idesc<T>(128, kTcKeyTile, false, false);
+      const uint32_t idesc_pv = umma_idesc<T>(128, D, false, true);
+      const uint32_t q_addr = smem_u32(q_sm), p_addr = smem_u32(p_sm);
+      auto issue_qk = [&](int i) {
+        const uint32_t k_addr = smem_u32(k_sm + (i % kTcStages) * KV_BYTES);
+        const uint32_t d_tmem = tmem + (uint32_t)((i & 1) * kTcKeyTile);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * PANEL_BYTES + (kk & 3) * 32;
+          umma_ss(d_tmem, umma_desc_kmajor(q_addr + off), umma_desc_kmajor(k_addr + off), idesc_qk, kk > 0);
+        }
+        umma_commit(s_full + (i & 1));
+      };
+      mbar_wait(q_full, 0, p.st);
+      mbar_wait(k_full, 0, p.st);
+      tc_fence_after_sync();
+      issue_qk(0);
+      for (int i = 0; i < ntiles; ++i) {
+        if (i + 1 < ntiles) {
+          const int n = i + 1;
+          mbar_wait(k_full + (n % kTcStages), (n / kTcStages) & 1, p.st);
+          if (n >= 2) mbar_wait(s_empty + (n & 1), ((n >> 1) - 1) & 1, p.st);
+          tc_fence_after_sync();
+          issue_qk(n);
+        }
+        mbar_wait(p_full, i & 1, p.st);
+        mbar_wait(v_full + (i % kTcStages), (i / kTcStages) & 1, p.st);
+        tc_fence_after_sync();
+        const uint32_t v_addr = smem_u32(v_sm + (i % kTcStages) * KV_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < kTcKeyTile / 16; ++kk) {
+          const uint32_t a_off = (kk >> 2) * PANEL_BYTES + (kk & 3) * 32;
+          umma_ss(tmem + 256, umma_desc_kmajor(p_addr + a_off), umma_desc_mnmajor(v_addr + kk * 2048, PANEL_BYTES), idesc_pv,
+                  i > 0 || kk > 0);
+        }
+        umma_commit(kv_empty + (i % kTcStages));
+        umma_commit(pv_done);
+      }
+    }
+  } else {
+    // ===================== softmax: thread r owns row r =====================
+    const int row = threadIdx.x;
+    const int tpos = q0 + (row >> p.logG);
+    const int head = h * p.G + (row & (p.G - 1));
+    const bool valid = tpos < Lq;
+    const int nvis = valid ? visible_keys_tc(tpos, Lk, p.window, p.stride, p.causal) : 0;
+    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    float m_ref = -INFINITY, l = 0.f;
+    for (int i = 0; i < ntiles; ++i) {
+      const int bsel = i & 1;
+      mbar_wait(s_full + bsel, (i >> 1) & 1, p.st);
+      tc_fence_after_sync();
+      uint32_t su[kTcKeyTile / 32][32];
+#pragma unroll
+      for (int c = 0; c < kTcKeyTile / 32; ++c) tmem_ld32(lane_base + bsel * kTcKeyTile + c * 32, su[c]);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_empty + bsel);
+
+      const int lim = nvis - i * kTcKeyTile;
+      float mt = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < kTcKeyTile; ++j) {
+        const float v = (j < lim) ? __uint_as_float(su[j >> 5][j & 31]) * p.scale2 : -INFINITY;
+        su[j >> 5][j & 31] = __float_as_uint(v);
+        mt = fmaxf(mt, v);
+      }
+      const bool need = mt > m_ref + 8.f;
+      float factor = 1.f;
+      if (need) {
+        factor = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - mt);
+        m_ref = mt;
+        l *= factor;
+      }
+      if (i > 0) {
+        mbar_wait(pv_done, (i - 1) & 1, p.st);  // P V of the previous tile is complete: O is stable, the P tile is free
+        tc_fence_after_sync();
+        if (__any_sync(0xffffffffu, need)) {
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(lane_base + 256 + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * factor);
+            tmem_st32(lane_base + 256 + c * 32, r);
+          }
+          tmem_st_wait();
+        }
+      }
+      const float msafe = (m_ref == -INFINITY) ? 0.f : m_ref;
+      const uint32_t prow = smem_u32(p_sm) + row * 128;
+      float lsum = 0.f;
+#pragma unroll
+      for (int c = 0; c < kTcKeyTile / 8; ++c) {  // 16-byte chunks of 8 keys
+        float pv[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          pv[j] = fast_exp2(__uint_as_float(su[(c * 8 + j) >> 5][(c * 8 + j) & 31]) - msafe);
+          lsum += pv[j];
+        }
+        const uint32_t addr = prow + (c >> 3) * PANEL_BYTES + (((c & 7) ^ (row & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(DT<T>::pack(pv[0], pv[1])),
+                     "r"(DT<T>::pack(pv[2], pv[3])), "r"(DT<T>::pack(pv[4], pv[5])), "r"(DT<T>::pack(pv[6], pv[7]))
+                     : "memory");
+      }
+      l += lsum;
+      fence_proxy_async();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    // ---- epilogue: O / l ----
+    if (ntiles > 0) {
+      mbar_wait(pv_done, (ntiles - 1) & 1, p.st);
+      tc_fence_after_sync();
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    if (valid) p.lse[(long long)(qs + tpos) * p.Hq + head] = l > 0.f ? m_ref + log2f(l) : -INFINITY;
+    T* orow = static_cast<T*>(p.o) + (long long)(qs + tpos) * p.o_sn + (long long)head * p.o_sh;
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t r[32];
+      if (ntiles > 0) {
+        tmem_ld32(lane_base + 256 + c * 32, r);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = 0u;
+      }
+      if (valid) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 out;
+          out.x = DT<T>::pack(__uint_as_float(r[q4 * 8 + 0]) * inv, __uint_as_float(r[q4 * 8 + 1]) * inv);
+          out.y = DT<T>::pack(__uint_as_float(r[q4 * 8 + 2]) * inv, __uint_as_float(r[q4 * 8 + 3]) * inv);
+          out.z = DT<T>::pack(__uint_as_float(r[q4 * 8 + 4]) * inv, __uint_as_float(r[q4 * 8 + 5]) * inv);
+          out.w = DT<T>::pack(__uint_as_float(r[q4 * 8 + 6]) * inv, __uint_as_float(r[q4 * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = out;
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem, 512);
+}
+
+template <typename T, int D>
+static int launch_dense_fwd_tc(const void* q, const void* k, const void* v, const long long* S, int Nq, int Nk, int max_seqlen_q,
+                               DenseFwdTcParams p, cudaStream_t stream) {
+  // S: q_n q_h k_n k_h v_n v_h o_n o_h
+  CUtensorMap tmQ, tmK, tmV;
+  const int QT = 128 / p.G;
+  int rc = make_tmap_3d(&tmQ, DT<T>::kTmapType, q, D, p.Hq, Nq, S[1], S[0], 64, p.G, QT);
+  if (rc) return rc;
+  rc = make_tmap_3d(&tmK, DT<T>::kTmapType, k, D, p.Hkv, Nk, S[3], S[2], 64, 1, kTcKeyTile);
+  if (rc) return rc;
+  rc = make_tmap_3d(&tmV, DT<T>::kTmapType, v, D, p.Hkv, Nk, S[5], S[4], 64, 1, kTcKeyTile);
+  if (rc) return rc;
+  const size_t smem = 1024 + 128 * D * 2 + 2 * kTcStages * kTcKeyTile * D * 2 + 128 * kTcKeyTile * 2 + 32 * sizeof(uint64_t);
+  auto kern = dense_fwd_tc_kernel<T, D>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return cuda_rc(e);
+  dim3 grid((max_seqlen_q + QT - 1) / QT, p.B, p.Hkv);
+  { LaunchScope ls_("dense_fwd_tc", stream); kern<<<grid, 192, smem, stream>>>(tmQ, tmK, tmV, p); }
+  return cuda_rc(cudaGetLastError());
+}
+
+// entry used by nsa_varlen_attn_fwd (dense_fwd.cu)
+int varlen_attn_fwd_tc(const void* q, const void* k, const void* v, const int* cu_q, const int* cu_k, void* o, float* lse,
+                       int total_q, int total_k, int batch, int max_seqlen_q, int Hq, int Hkv, int head_dim, int causal,
+                       int window, int stride, const long long* strides, float sm_scale, int dtype, cudaStream_t stream) {
+  DenseFwdTcParams p;
+  p.o = o; p.lse = lse; p.cu_q = cu_q; p.cu_k = cu_k;
+  p.o_sn = strides[6]; p.o_sh = strides[7];
+  p.B = batch; p.Hq = Hq; p.Hkv = Hkv; p.G = Hq / Hkv;
+  p.logG = 0;
+  while ((1 << p.logG) < p.G) ++p.logG;
+  p.window = window; p.stride = stride; p.causal = causal;
+  p.scale2 = sm_scale * kLog2e;
+  p.st.word = status_word();
+  return NSA_DISPATCH_T_D(dtype, head_dim, launch_dense_fwd_tc, q, k, v, strides, total_q, total_k, max_seqlen_q, p, stream);
+}
+
+}  // namespace nsa
