@@ -14,10 +14,13 @@
 //               dimension, so no per-head dK/dV copies exist.  Partial results of the CTAs that
 //               share a key tile are added with fp32 red.global into a zeroed accumulator and
 //               converted to the storage type at the end.
+#include <cstdlib>
+
 #include "attn_tile.cuh"
 #include "dispatch.h"
 #include "host_util.h"
 #include "nsa_b200.h"
+#include "attn_bwd.h"
 
 namespace nsa {
 
@@ -418,23 +421,6 @@ __global__ void index_scan_kernel(IndexParams p) {
 // ------------------------------------------------------------------------------------------------
 // dK / dV pass
 // ------------------------------------------------------------------------------------------------
-struct DkdvParams {
-  const float2* ld;    // [Nq, Hq]
-  float* dk32;         // [Nk, Hkv, D] fp32 accumulators (zeroed)
-  float* dv32;
-  const int* cu_q;
-  const int* cu_k;      // dense: compressed cu; sparse: same as cu_q
-  // sparse
-  const int* cu_blocks;
-  const int* offsets;
-  const int* item_base;
-  const int* list;
-  int B, Hq, Hkv, G, TB, chunk, block_size;
-  int window, stride, causal;
-  float scale2, sm_scale;
-  Status st;
-};
-
 constexpr int kSlots = 2;        // tokens per pipeline stage
 constexpr int kBwdStages = 4;
 
@@ -677,6 +663,12 @@ __global__ void convert_rows_kernel(const float* __restrict__ src, void* dst, lo
   *reinterpret_cast<uint2*>(static_cast<T*>(dst) + n * d_sn + (long long)h * d_sh + c * 4) = out;
 }
 
+// NSA_B200_LEGACY_MMA=1 keeps the mma.sync kernels selectable for A/B measurements
+static bool legacy_mma() {
+  static const bool v = [] { const char* e = getenv("NSA_B200_LEGACY_MMA"); return e && e[0] == '1'; }();
+  return v;
+}
+
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 template <typename T, int D, bool SPARSE>
@@ -766,7 +758,13 @@ static int run_dense_bwd(const void* q, const void* k, const void* v, const void
   d.scale2 = p.scale2; d.sm_scale = sm_scale; d.st = p.st;
   const long long ds[8] = {S[0], S[1], S[2], S[3], S[4], S[5], S[8], S[9]};
   dim3 grid((max_q + chunk - 1) / chunk, (max_k + kKeyTile - 1) / kKeyTile, batch * Hkv);
-  int rc = launch_dkdv<T, D, false>(q, dout, k, v, ds, total_q, total_k, grid, d, stream);
+  int rc;
+  if constexpr (D == 128) {
+    rc = (G >= 4 && !legacy_mma()) ? launch_dkdv_tc<T, false>(q, dout, k, v, ds, total_q, total_k, grid, d, stream)
+                                   : launch_dkdv<T, D, false>(q, dout, k, v, ds, total_q, total_k, grid, d, stream);
+  } else {
+    rc = launch_dkdv<T, D, false>(q, dout, k, v, ds, total_q, total_k, grid, d, stream);
+  }
   if (rc) return rc;
   const long long n4 = (long long)total_k * Hkv * (D / 4);
   { LaunchScope ls_("convert_dk", stream); convert_rows_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(dk32, dk, total_k, Hkv, D, S[12], S[13]); }
@@ -858,7 +856,13 @@ static int run_sparse_bwd(const void* q, const void* k, const void* v, const voi
   // upper bound on work items: every selection in a full chunk, plus one partial chunk per (head, block)
   const long long max_items = ((long long)Hkv * N * topk) / kSparseChunk + (long long)Hkv * TB;
   dim3 grid((unsigned)max_items, block_size / kKeyTile, 1);
-  int rc = launch_dkdv<T, D, true>(q, dout, k, v, ds, N, N, grid, d, stream);
+  int rc;
+  if constexpr (D == 128) {
+    rc = (G >= 4 && (G & (G - 1)) == 0 && !legacy_mma()) ? launch_dkdv_tc<T, true>(q, dout, k, v, ds, N, N, grid, d, stream)
+                                                         : launch_dkdv<T, D, true>(q, dout, k, v, ds, N, N, grid, d, stream);
+  } else {
+    rc = launch_dkdv<T, D, true>(q, dout, k, v, ds, N, N, grid, d, stream);
+  }
   if (rc) return rc;
   const long long n4 = (long long)N * Hkv * (D / 4);
   { LaunchScope ls_("convert_dk", stream); convert_rows_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(dk32, dk, N, Hkv, D, S[12], S[13]); }

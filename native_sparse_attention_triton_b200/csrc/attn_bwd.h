@@ -1,0 +1,34 @@
+// Parameter block shared by the two implementations of the dK/dV pass (mma.sync and tcgen05).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+
+namespace nsa {
+
+struct DkdvParams {
+  const float2* ld;    // [Nq, Hq]
+  float* dk32;         // [Nk, Hkv, D] fp32 accumulators (zeroed)
+  float* dv32;
+  const int* cu_q;
+  const int* cu_k;      // dense: compressed cu; sparse: same as cu_q
+  // sparse
+  const int* cu_blocks;
+  const int* offsets;
+  const int* item_base;
+  const int* list;
+  int B, Hq, Hkv, G, TB, chunk, block_size;
+  int window, stride, causal;
+  float scale2, sm_scale;
+  Status st;
+};
+
+
+// tcgen05 implementation of the dK/dV pass (attn_bwd_tc.cu); head_dim 128 only.
+// strides: q_n q_h k_n k_h v_n v_h do_n do_h (elements)
+template <typename T, bool SPARSE>
+int launch_dkdv_tc(const void* q, const void* dout, const void* k, const void* v, const long long* strides, int Nq, int Nk,
+                   dim3 grid, DkdvParams p, cudaStream_t stream);
+
+}  // namespace nsa
