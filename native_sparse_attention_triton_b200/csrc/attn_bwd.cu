@@ -50,7 +50,7 @@ __device__ __forceinline__ void dq_tile(const uint32_t (&qf)[D / 16][4], const u
       for (int e = 0; e < 4; ++e) {
         const int r = e >> 1;
         const int col = 32 * half + j * 8 + c0 + (e & 1);
-        const float pr = col < lim[r] ? fast_exp2(s[j][e] * scale2 - lse2[r]) : 0.f;
+        const float pr = masked_exp2(col < lim[r], s[j][e] * scale2 - lse2[r]);
         s[j][e] = pr * (dp[j][e] - delta[r]) * sm_scale;
       }
     }
@@ -476,12 +476,12 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     qs = __ldg(p.cu_q + b);
     Lq = __ldg(p.cu_q + b + 1) - qs;
     const int ks0 = __ldg(p.cu_k + b), Lk = __ldg(p.cu_k + b + 1) - ks0;
-    kpos = blockIdx.y * kKeyTile;
+    kpos = blockIdx.x * kKeyTile;  // key tiles vary fastest: CTAs that run together share a token chunk in L2
     if (kpos >= Lk) return;
     krow0 = ks0 + kpos;
     kvalid = min(kKeyTile, Lk - kpos);
     const int t_first = p.causal ? kpos * p.stride + p.window - 1 : 0;
-    const int c_lo = blockIdx.x * p.chunk;
+    const int c_lo = blockIdx.y * p.chunk;
     tok_begin = max(c_lo, t_first);
     tok_count = min(c_lo + p.chunk, Lq) - tok_begin;
   }
@@ -610,7 +610,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
           const int head = j * 8 + c0 + (e & 1);
           const float2 ldv = ldp[head];
           const bool vis = tpos >= need[r] && head < p.G;   // tpos = -1 for an empty slot
-          const float pr = vis ? fast_exp2(st_[2 * sl + j][e] * p.scale2 - ldv.x) : 0.f;
+          const float pr = masked_exp2(vis, st_[2 * sl + j][e] * p.scale2 - ldv.x);
           st_[2 * sl + j][e] = pr;
           dp_[2 * sl + j][e] = vis ? pr * (dp_[2 * sl + j][e] - ldv.y) * p.sm_scale : 0.f;
         }
@@ -752,12 +752,12 @@ static int run_dense_bwd(const void* q, const void* k, const void* v, const void
   d.cu_blocks = nullptr; d.offsets = nullptr; d.item_base = nullptr; d.list = nullptr;
   d.B = batch; d.Hq = Hq; d.Hkv = Hkv; d.G = G; d.TB = 0; d.block_size = kKeyTile;
   int chunk = 256;
-  while (chunk < 4096 && chunk * 16 < max_q) chunk <<= 1;
+  while (chunk < 1024 && chunk * 16 < max_q) chunk <<= 1;
   d.chunk = chunk;
   d.window = window; d.stride = stride; d.causal = causal;
   d.scale2 = p.scale2; d.sm_scale = sm_scale; d.st = p.st;
   const long long ds[8] = {S[0], S[1], S[2], S[3], S[4], S[5], S[8], S[9]};
-  dim3 grid((max_q + chunk - 1) / chunk, (max_k + kKeyTile - 1) / kKeyTile, batch * Hkv);
+  dim3 grid((max_k + kKeyTile - 1) / kKeyTile, (max_q + chunk - 1) / chunk, batch * Hkv);
   int rc;
   if constexpr (D == 128) {
     rc = (G >= 4 && !legacy_mma()) ? launch_dkdv_tc<T, false>(q, dout, k, v, ds, total_q, total_k, grid, d, stream)

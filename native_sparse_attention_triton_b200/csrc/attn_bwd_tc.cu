@@ -91,12 +91,12 @@ dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     qs = __ldg(p.cu_q + b);
     Lq = __ldg(p.cu_q + b + 1) - qs;
     const int ks0 = __ldg(p.cu_k + b), Lk = __ldg(p.cu_k + b + 1) - ks0;
-    kpos = blockIdx.y * KT;
+    kpos = blockIdx.x * KT;  // key tiles vary fastest: CTAs that run together share a token chunk in L2
     if (kpos >= Lk) return;
     krow0 = ks0 + kpos;
     kvalid = min(KT, Lk - kpos);
     const int t_first = p.causal ? kpos * p.stride + p.window - 1 : 0;
-    const int c_lo = blockIdx.x * p.chunk;
+    const int c_lo = blockIdx.y * p.chunk;
     tok_begin = max(c_lo, t_first);
     tok_count = min(c_lo + p.chunk, Lq) - tok_begin;
   }
@@ -269,7 +269,7 @@ dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           const int col = c * 8 + j;
           const float sv = __uint_as_float(su[col >> 5][col & 31]);
           const float dp = __uint_as_float(du[col >> 5][col & 31]);
-          const float pr = col < lim ? fast_exp2(sv * p.scale2 - ldv.x) : 0.f;
+          const float pr = masked_exp2(col < lim, sv * p.scale2 - ldv.x);
           pv[j] = pr;
           dv[j] = col < lim ? pr * (dp - ldv.y) * p.sm_scale : 0.f;
         }

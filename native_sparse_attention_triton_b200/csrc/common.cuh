@@ -86,8 +86,15 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
-  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));  // pure: the compiler may schedule many of them back to back
   return y;
+}
+
+// 2^x where `keep` holds, else 0.  The exponential is evaluated unconditionally and the result selected, so a
+// per-thread mask never turns into a divergent branch around the MUFU instruction.
+__device__ __forceinline__ float masked_exp2(bool keep, float x) {
+  const float e = fast_exp2(x);
+  return keep ? e : 0.f;
 }
 
 __device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }

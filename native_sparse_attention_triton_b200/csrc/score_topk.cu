@@ -12,29 +12,16 @@
 // 16 rows = (16/G tokens) x (G heads), sums over heads with lane shuffles inside the mma
 // accumulator layout, folds key scores into per-token block scores held in shared memory, and
 // selects with warp-level argmax rounds.
+#include <cstdlib>
+
 #include "attn_tile.cuh"
 #include "dispatch.h"
 #include "host_util.h"
 #include "nsa_b200.h"
 #include "topk_select.cuh"
+#include "score_topk.h"
 
 namespace nsa {
-
-struct ScoreParams {
-  const void* q;
-  const float* lse;  // [Nq, Hq] base-2
-  int* topk_idx;
-  const int* cu_q;
-  const int* cu_k;
-  long long q_sn, q_sh;
-  long long t_sh, t_sn, t_sk;
-  int B, Hq, Hkv, G, logG;
-  int window, stride, block_size;
-  int topk_out, init_blocks, local_blocks, nb_pad;
-  int nwarps;
-  float scale2;
-  Status st;
-};
 
 __device__ __forceinline__ int visible_keys_c(int t, int Lk, int window, int stride) {
   if (t < window - 1) return 0;
@@ -140,8 +127,8 @@ score_topk_kernel(const __grid_constant__ CUtensorMap tmK, ScoreParams p) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int col = j * 8 + c0 + e;
-          float v0 = col < lim0 ? fast_exp2(sc[j][e] * p.scale2 - lse2[0]) : 0.f;
-          float v1 = col < lim1 ? fast_exp2(sc[j][e + 2] * p.scale2 - lse2[1]) : 0.f;
+          float v0 = masked_exp2(col < lim0, sc[j][e] * p.scale2 - lse2[0]);
+          float v1 = masked_exp2(col < lim1, sc[j][e + 2] * p.scale2 - lse2[1]);
           if (p.logG == 4) v0 += v1;
           for (int sh = 0; sh < nshuf; ++sh) {
             v0 += __shfl_xor_sync(0xffffffffu, v0, 4 << sh);
@@ -243,6 +230,14 @@ extern "C" int nsa_compressed_attn_topk(const void* q, const void* k, const floa
   p.scale2 = sm_scale * kLog2e;
   p.st.word = status_word();
   if ((p.q_sn | p.q_sh) % 8 || !aligned16(q)) return kInvalid;
+  {
+    static const bool legacy = [] { const char* e = getenv("NSA_B200_LEGACY_MMA"); return e && e[0] == '1'; }();
+    if (!legacy) {
+      const int rc = score_topk_tc(q, k, strides[2], strides[3], total_q, total_k, max_seqlen_q, head_dim, dtype, p,
+                                   static_cast<cudaStream_t>(stream));
+      if (rc != kUnsupported) return rc;  // otherwise fall through to the mma.sync kernel
+    }
+  }
   return NSA_DISPATCH_T_D(dtype, head_dim, launch_score_topk, k, strides[2], strides[3], total_k, max_seqlen_q, p,
                           static_cast<cudaStream_t>(stream));
 }
