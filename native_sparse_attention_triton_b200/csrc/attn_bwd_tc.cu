@@ -10,10 +10,10 @@
 // summed inside the MMA.  S and dP are double-buffered in TMEM (tile i+1 is computed while the softmax
 // threads work on tile i); dV^T and dK^T stay in TMEM for the whole CTA and are added to the fp32
 // accumulators in global memory at the end.
-//   warps 0..3 : thread r owns row r: P = exp2(S*scale - lse), dS = P (dP - delta) scale, written as
-//                16-bit [rows][keys] tiles; at the end thread d drains column d of dV / dK
-//   warp 4     : TMA producer (Q and dO rows of the tile, one box per token for gathered tokens)
-//   warp 5     : TMEM allocation, MMA issue (one thread)
+//   warps 0..7 : two threads per row (32 key columns each): P = exp2(S*scale - lse), dS = P (dP - delta) scale,
+//                written as 16-bit [rows][keys] tiles; at the end they drain dV / dK from TMEM
+//   warp 8     : TMA producer (Q and dO rows of the tile, one box per token for gathered tokens)
+//   warp 9     : TMEM allocation, MMA issue (one thread)
 // TMEM columns: S0 [0,64) S1 [64,128) dP0 [128,192) dP1 [192,256) dV^T [256,320) dK^T [320,384).
 #include "attn_bwd.h"
 #include "attn_tile.cuh"
@@ -25,7 +25,7 @@ namespace nsa {
 constexpr int kRowStages = 2;
 
 template <typename T, bool SPARSE>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, DkdvParams p) {
   constexpr int D = 128;
@@ -111,9 +111,9 @@ dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(sdp_full + s, 1);
-      mbar_init(sdp_empty + s, 4);
+      mbar_init(sdp_empty + s, 8);
     }
-    mbar_init(pds_full, 4);
+    mbar_init(pds_full, 8);
     mbar_init(pds_empty, 1);
     mbar_init(all_done, 1);
     fence_barrier_init();
@@ -123,7 +123,7 @@ dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   for (int i = threadIdx.x; i < kRowStages * 2 * ROW_BYTES / 16; i += blockDim.x)
     reinterpret_cast<uint4*>(ring)[i] = make_uint4(0u, 0u, 0u, 0u);
   fence_proxy_async();
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -132,7 +132,7 @@ dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   tc_fence_after_sync();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ===================== producer =====================
     if (lane == 0) {
       mbar_expect_tx(kv_full, 2 * KV_BYTES);
@@ -181,7 +181,7 @@ dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ===================== MMA issuer =====================
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc<T>(128, KT, false, false);
@@ -203,20 +203,7 @@ dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         umma_commit(sdp_full + (i & 1));
       };
-      mbar_wait(kv_full, 0, p.st);
-      mbar_wait(row_full, 0, p.st);
-      tc_fence_after_sync();
-      issue_sdp(0);
-      for (int i = 0; i < ntiles; ++i) {
-        if (i + 1 < ntiles) {
-          const int n = i + 1;
-          mbar_wait(row_full + (n % kRowStages), (n / kRowStages) & 1, p.st);
-          if (n >= 2) mbar_wait(sdp_empty + (n & 1), ((n >> 1) - 1) & 1, p.st);
-          tc_fence_after_sync();
-          issue_sdp(n);
-        }
-        mbar_wait(pds_full, i & 1, p.st);
-        tc_fence_after_sync();
+      auto issue_dvdk = [&](int i) {
         const uint32_t q_addr = smem_u32(ring + (i % kRowStages) * 2 * ROW_BYTES);
         const uint32_t do_addr = q_addr + ROW_BYTES;
 #pragma unroll
@@ -229,24 +216,49 @@ dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                   idesc_t, i > 0 || kk > 0);
         umma_commit(row_empty + (i % kRowStages));
         umma_commit(pds_empty);
+      };
+      mbar_wait(kv_full, 0, p.st);
+      // Two independent streams of work share the tensor pipe: S/dP of tile ns (needs the tile's rows and a free TMEM
+      // buffer) and dV/dK of tile nd (needs P and dS of that tile).  Whichever is ready is issued; neither blocks the other.
+      int ns = 0, nd = 0;
+      long long t0 = clock64();
+      while (nd < ntiles) {
+        bool progressed = false;
+        if (ns < ntiles && ns - nd < 2 && mbar_try_wait(row_full + (ns % kRowStages), (ns / kRowStages) & 1) &&
+            (ns < 2 || mbar_try_wait(sdp_empty + (ns & 1), ((ns >> 1) - 1) & 1))) {
+          tc_fence_after_sync();
+          issue_sdp(ns);
+          ++ns;
+          progressed = true;
+        }
+        if (nd < ns && mbar_try_wait(pds_full, nd & 1)) {
+          tc_fence_after_sync();
+          issue_dvdk(nd);
+          ++nd;
+          progressed = true;
+        }
+        if (progressed) {
+          t0 = clock64();
+        } else if (clock64() - t0 > (1ll << 30) || (p.st.word && (*reinterpret_cast<volatile int*>(p.st.word) & kErrWaitTimeout))) {
+          p.st.raise(kErrWaitTimeout);  // bounded: give up instead of spinning forever
+          break;
+        }
       }
       umma_commit(all_done);
     }
   } else {
-    // ===================== softmax / dS threads: thread r owns row r =====================
-    const int row = threadIdx.x;
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    // ===================== softmax / dS threads: two threads per row (32 of the 64 key columns each) =====================
+    const int half = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     for (int i = 0; i < ntiles; ++i) {
       const int bsel = i & 1, s = i % kRowStages;
       mbar_wait(row_full + s, (i / kRowStages) & 1, p.st);  // acquire the producer's per-row metadata of this stage
       mbar_wait(sdp_full + bsel, (i >> 1) & 1, p.st);
       tc_fence_after_sync();
-      uint32_t su[2][32], du[2][32];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        tmem_ld32(lane_base + bsel * KT + c * 32, su[c]);
-        tmem_ld32(lane_base + 128 + bsel * KT + c * 32, du[c]);
-      }
+      uint32_t su[32], du[32];
+      tmem_ld32(lane_base + bsel * KT + half * 32, su);
+      tmem_ld32(lane_base + 128 + bsel * KT + half * 32, du);
       tmem_ld_wait();
       tc_fence_before_sync();
       __syncwarp();
@@ -259,54 +271,53 @@ dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         if (!p.causal) lim = kvalid;
         else if (tpos >= p.window - 1) lim = max(0, min(kvalid, (tpos - (p.window - 1)) / p.stride - kpos + 1));
       }
+      lim -= half * 32;  // relative to this thread's first column
+      const float nlse = -ldv.x, delta = ldv.y;
+      uint32_t pw[16], dw[16];
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        const float p0 = masked_exp2(j < lim, fmaf(__uint_as_float(su[j]), p.scale2, nlse));
+        const float p1 = masked_exp2(j + 1 < lim, fmaf(__uint_as_float(su[j + 1]), p.scale2, nlse));
+        const float d0 = p0 * (__uint_as_float(du[j]) - delta) * p.sm_scale;
+        const float d1 = p1 * (__uint_as_float(du[j + 1]) - delta) * p.sm_scale;
+        pw[j >> 1] = DT<T>::pack(p0, p1);
+        dw[j >> 1] = DT<T>::pack(d0, d1);
+      }
       if (i > 0) mbar_wait(pds_empty, (i - 1) & 1, p.st);  // the previous tile's dV/dK products have read P and dS
       const uint32_t prow = smem_u32(p_sm) + row * 128, dsrow = smem_u32(ds_sm) + row * 128;
 #pragma unroll
-      for (int c = 0; c < KT / 8; ++c) {
-        float pv[8], dv[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int col = c * 8 + j;
-          const float sv = __uint_as_float(su[col >> 5][col & 31]);
-          const float dp = __uint_as_float(du[col >> 5][col & 31]);
-          const float pr = masked_exp2(col < lim, sv * p.scale2 - ldv.x);
-          pv[j] = pr;
-          dv[j] = col < lim ? pr * (dp - ldv.y) * p.sm_scale : 0.f;
-        }
-        const uint32_t sw = ((c ^ (row & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(prow + sw), "r"(DT<T>::pack(pv[0], pv[1])),
-                     "r"(DT<T>::pack(pv[2], pv[3])), "r"(DT<T>::pack(pv[4], pv[5])), "r"(DT<T>::pack(pv[6], pv[7])) : "memory");
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(dsrow + sw), "r"(DT<T>::pack(dv[0], dv[1])),
-                     "r"(DT<T>::pack(dv[2], dv[3])), "r"(DT<T>::pack(dv[4], dv[5])), "r"(DT<T>::pack(dv[6], dv[7])) : "memory");
+      for (int c4 = 0; c4 < 4; ++c4) {
+        const uint32_t sw = (((half * 4 + c4) ^ (row & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(prow + sw), "r"(pw[c4 * 4]), "r"(pw[c4 * 4 + 1]),
+                     "r"(pw[c4 * 4 + 2]), "r"(pw[c4 * 4 + 3]) : "memory");
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(dsrow + sw), "r"(dw[c4 * 4]), "r"(dw[c4 * 4 + 1]),
+                     "r"(dw[c4 * 4 + 2]), "r"(dw[c4 * 4 + 3]) : "memory");
       }
       fence_proxy_async();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
     }
-    // ---- drain: thread d holds column d of dV and dK for the 64 keys ----
+    // ---- drain: thread (d, half) holds column d of dV and dK for 32 of the 64 keys ----
     mbar_wait(all_done, 0, p.st);
     tc_fence_after_sync();
-    const int d = threadIdx.x;
+    const int d = row;
 #pragma unroll
     for (int which = 0; which < 2; ++which) {
       float* dst = (which == 0 ? p.dv32 : p.dk32) + ((size_t)krow0 * p.Hkv + h) * D + d;
+      uint32_t r[32];
+      tmem_ld32(lane_base + 256 + which * 64 + half * 32, r);
+      tmem_ld_wait();
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32(lane_base + 256 + which * 64 + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int key = c * 32 + j;
-          if (key < kvalid) atomicAdd(dst + (size_t)key * p.Hkv * D, __uint_as_float(r[j]));
-        }
+      for (int j = 0; j < 32; ++j) {
+        const int key = half * 32 + j;
+        if (key < kvalid) atomicAdd(dst + (size_t)key * p.Hkv * D, __uint_as_float(r[j]));
       }
     }
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem, 512);
+  if (warp == 9) tmem_dealloc(tmem, 512);
 }
 
 template <typename T, bool SPARSE>
@@ -329,7 +340,7 @@ int launch_dkdv_tc(const void* q, const void* dout, const void* k, const void* v
   auto kern = dkdv_tc_kernel<T, SPARSE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_rc(e);
-  { LaunchScope ls_(SPARSE ? "sparse_dkdv_tc" : "dense_dkdv_tc", stream); kern<<<grid, 192, smem, stream>>>(tmQ, tmDO, tmK, tmV, p); }
+  { LaunchScope ls_(SPARSE ? "sparse_dkdv_tc" : "dense_dkdv_tc", stream); kern<<<grid, 320, smem, stream>>>(tmQ, tmDO, tmK, tmV, p); }
   return cuda_rc(cudaGetLastError());
 }
 
