@@ -88,22 +88,6 @@ __device__ __forceinline__ void row_delta(const T* o0, const T* o1, const uint32
 // ------------------------------------------------------------------------------------------------
 // dense dQ
 // ------------------------------------------------------------------------------------------------
-struct DenseBwdParams {
-  const void* q;
-  const void* o;
-  const void* dout;
-  const float* lse;
-  float2* ld;  // [Nq, Hq] (lse, delta) written by the dQ pass
-  void* dq;
-  const int* cu_q;
-  const int* cu_k;
-  long long q_sn, q_sh, o_sn, o_sh, do_sn, do_sh, dq_sn, dq_sh;
-  int B, Hq, Hkv, G, logG;
-  int window, stride, causal;
-  float scale2, sm_scale;
-  Status st;
-};
-
 __device__ __forceinline__ int visible_keys_b(int t, int Lk, int window, int stride, int causal) {
   if (!causal) return Lk;
   if (t < window - 1) return 0;
@@ -729,6 +713,11 @@ static int run_dense_bwd(const void* q, const void* k, const void* v, const void
   p.window = window; p.stride = stride; p.causal = causal;
   p.scale2 = sm_scale * kLog2e; p.sm_scale = sm_scale;
   p.st.word = status_word();
+  if (!legacy_mma()) {
+    const int dt = DT<T>::kTmapType == CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 ? NSA_DTYPE_BF16 : NSA_DTYPE_FP16;
+    const int rc = dense_dq_tc(k, v, S[2], S[3], S[4], S[5], total_q, total_k, max_q, D, dt, p, stream);
+    if (rc) return rc;
+  } else
   {
     constexpr int WARPS = 8;
     constexpr int STAGES = (D == 128) ? 4 : 6;

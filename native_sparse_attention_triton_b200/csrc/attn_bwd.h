@@ -25,6 +25,27 @@ struct DkdvParams {
 };
 
 
+// dQ pass of dense strided-causal attention
+struct DenseBwdParams {
+  const void* q;
+  const void* o;
+  const void* dout;
+  const float* lse;
+  float2* ld;  // [Nq, Hq] (lse, delta) written by the dQ pass
+  void* dq;
+  const int* cu_q;
+  const int* cu_k;
+  long long q_sn, q_sh, o_sn, o_sh, do_sn, do_sh, dq_sn, dq_sh;
+  int B, Hq, Hkv, G, logG;
+  int window, stride, causal;
+  float scale2, sm_scale;
+  Status st;
+};
+
+// tcgen05 implementation of the dense dQ pass (dense_dq_tc.cu).  k/v strides in elements.
+int dense_dq_tc(const void* k, const void* v, long long k_sn, long long k_sh, long long v_sn, long long v_sh, int total_q,
+                int total_k, int max_seqlen_q, int head_dim, int dtype, DenseBwdParams p, cudaStream_t stream);
+
 // tcgen05 implementation of the dK/dV pass (attn_bwd_tc.cu); head_dim 128 only.
 // strides: q_n q_h k_n k_h v_n v_h do_n do_h (elements)
 template <typename T, bool SPARSE>
