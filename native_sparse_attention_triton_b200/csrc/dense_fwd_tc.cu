@@ -2,15 +2,17 @@
 // cores (tcgen05.mma, accumulators in tensor memory).
 //
 // CTA = 128 rows = (128/G query tokens) x (G query heads of one KV head), key tiles of 128.
-//   warp 4      : TMA producer (Q once, then K and V tiles through a 2-stage ring)
-//   warp 5      : allocates TMEM; one elected thread issues S = Q K^T (SMEM x SMEM -> TMEM) and
-//                 O += P V (P from SMEM, V read MN-major) and commits to mbarriers
-//   warps 0..3  : softmax.  Thread r owns row r (TMEM lane r): it reads its 128 logits with
-//                 tcgen05.ld, keeps a lazily-updated reference maximum (O and l are rescaled only
-//                 when the row maximum grows by more than 2^8), writes P as 16-bit into the
-//                 128B-swizzled SMEM tile the P V instruction reads, and finally normalises O.
-// S is double-buffered in TMEM so that Q K^T of tile i+1 overlaps the softmax of tile i.
-// TMEM columns: [0,128) S0, [128,256) S1, [256,256+D) O.
+//   warp 8      : TMA producer (Q once, then K and V tiles through a 3-stage ring)
+//   warp 9      : allocates TMEM; one elected thread issues S = Q K^T (SMEM x SMEM -> TMEM) and
+//                 O += P V (P read from TMEM, V from SMEM MN-major) and commits to mbarriers
+//   warps 0..7  : softmax.  Two threads share a row (TMEM lane), 64 key columns each: they read their logits with
+//                 tcgen05.ld, exchange the row maximum through shared memory, keep a lazily-updated reference maximum (O and l are rescaled only
+//                 when the row maximum grows by more than 2^8), writes P as 16-bit pairs back into
+//                 tensor memory over the logits (tcgen05.st) where the P V instruction reads its A
+//                 operand -- P never touches shared memory -- and finally normalises O.
+// S/P is double-buffered in TMEM so that Q K^T of tile i+1 overlaps the softmax of tile i; the tensor pipe
+// executes one thread's MMAs in issue order, so Q K^T of tile i+2 cannot overtake P V of tile i.
+// TMEM columns: [0,128) S0/P0, [128,256) S1/P1, [256,256+D) O.
 #include "attn_tile.cuh"
 #include "dispatch.h"
 #include "host_util.h"
@@ -38,33 +40,33 @@ __device__ __forceinline__ int visible_keys_tc(int t, int Lk, int window, int st
 }
 
 constexpr int kTcKeyTile = 128;
-constexpr int kTcStages = 2;
+constexpr int kTcKStages = 3;  // a K tile is free as soon as its Q K^T is done
+constexpr int kTcVStages = 2;  // a V tile is free when its P V is done
 
 template <typename T, int D>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, DenseFwdTcParams p) {
   constexpr int PANELS = D / 64;
   constexpr int PANEL_BYTES = 128 * 128;            // 128 rows x 128 B
   constexpr int Q_BYTES = 128 * D * 2;
   constexpr int KV_BYTES = kTcKeyTile * D * 2;      // one K or V tile
-  constexpr int P_BYTES = 128 * kTcKeyTile * 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_sm = smem;
   uint8_t* k_sm = q_sm + Q_BYTES;
-  uint8_t* v_sm = k_sm + kTcStages * KV_BYTES;
-  uint8_t* p_sm = v_sm + kTcStages * KV_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_sm + P_BYTES);
+  uint8_t* v_sm = k_sm + kTcKStages * KV_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_sm + kTcVStages * KV_BYTES);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;
-  uint64_t* v_full = k_full + kTcStages;
-  uint64_t* kv_empty = v_full + kTcStages;
-  uint64_t* s_full = kv_empty + kTcStages;
-  uint64_t* s_empty = s_full + 2;
-  uint64_t* p_full = s_empty + 2;
+  uint64_t* k_empty = k_full + kTcKStages;
+  uint64_t* v_full = k_empty + kTcKStages;
+  uint64_t* v_empty = v_full + kTcVStages;
+  uint64_t* s_full = v_empty + kTcVStages;
+  uint64_t* p_full = s_full + 2;
   uint64_t* pv_done = p_full + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+  float* xch = reinterpret_cast<float*>(tmem_slot + 2);  // [2][256] row-maximum / row-sum exchange between the two threads of a row
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.y, h = blockIdx.z;
@@ -79,20 +81,20 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < kTcStages; ++s) {
+    for (int s = 0; s < kTcKStages; ++s) {
       mbar_init(k_full + s, 1);
+      mbar_init(k_empty + s, 1);
+    }
+    for (int s = 0; s < kTcVStages; ++s) {
       mbar_init(v_full + s, 1);
-      mbar_init(kv_empty + s, 1);
+      mbar_init(v_empty + s, 1);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(s_full + s, 1);
-      mbar_init(s_empty + s, 4);
-    }
-    mbar_init(p_full, 4);
+    for (int s = 0; s < 2; ++s) mbar_init(s_full + s, 1);
+    mbar_init(p_full, 8);
     mbar_init(pv_done, 1);
     fence_barrier_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -101,39 +103,47 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   tc_fence_after_sync();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ===================== TMA producer =====================
     if (lane == 0 && ntiles > 0) {
       mbar_expect_tx(q_full, Q_BYTES);
 #pragma unroll
       for (int pn = 0; pn < PANELS; ++pn) tma_load_3d(q_sm + pn * PANEL_BYTES, &tmQ, q_full, pn * 64, h * p.G, qs + q0);
-      for (int i = 0; i < ntiles; ++i) {
-        const int s = i % kTcStages;
-        if (i >= kTcStages) mbar_wait(kv_empty + s, ((i / kTcStages) - 1) & 1, p.st);
-        mbar_expect_tx(k_full + s, KV_BYTES);
+      // K runs one tile ahead of V: tile i's V is requested after tile i+1's K
+      for (int i = 0; i <= ntiles; ++i) {
+        if (i < ntiles) {
+          const int s = i % kTcKStages;
+          if (i >= kTcKStages) mbar_wait(k_empty + s, ((i / kTcKStages) - 1) & 1, p.st);
+          mbar_expect_tx(k_full + s, KV_BYTES);
 #pragma unroll
-        for (int pn = 0; pn < PANELS; ++pn)
-          tma_load_3d(k_sm + s * KV_BYTES + pn * PANEL_BYTES, &tmK, k_full + s, pn * 64, h, ksq + i * kTcKeyTile);
-        mbar_expect_tx(v_full + s, KV_BYTES);
+          for (int pn = 0; pn < PANELS; ++pn)
+            tma_load_3d(k_sm + s * KV_BYTES + pn * PANEL_BYTES, &tmK, k_full + s, pn * 64, h, ksq + i * kTcKeyTile);
+        }
+        if (i >= 1) {
+          const int j = i - 1, s = j % kTcVStages;
+          if (j >= kTcVStages) mbar_wait(v_empty + s, ((j / kTcVStages) - 1) & 1, p.st);
+          mbar_expect_tx(v_full + s, KV_BYTES);
 #pragma unroll
-        for (int pn = 0; pn < PANELS; ++pn)
-          tma_load_3d(v_sm + s * KV_BYTES + pn * PANEL_BYTES, &tmV, v_full + s, pn * 64, h, ksq + i * kTcKeyTile);
+          for (int pn = 0; pn < PANELS; ++pn)
+            tma_load_3d(v_sm + s * KV_BYTES + pn * PANEL_BYTES, &tmV, v_full + s, pn * 64, h, ksq + j * kTcKeyTile);
+        }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ===================== MMA issuer =====================
     if (lane == 0 && ntiles > 0) {
       const uint32_t idesc_qk = umma_idesc<T>(128, kTcKeyTile, false, false);
       const uint32_t idesc_pv = umma_idesc<T>(128, D, false, true);
-      const uint32_t q_addr = smem_u32(q_sm), p_addr = smem_u32(p_sm);
+      const uint32_t q_addr = smem_u32(q_sm);
       auto issue_qk = [&](int i) {
-        const uint32_t k_addr = smem_u32(k_sm + (i % kTcStages) * KV_BYTES);
+        const uint32_t k_addr = smem_u32(k_sm + (i % kTcKStages) * KV_BYTES);
         const uint32_t d_tmem = tmem + (uint32_t)((i & 1) * kTcKeyTile);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * PANEL_BYTES + (kk & 3) * 32;
           umma_ss(d_tmem, umma_desc_kmajor(q_addr + off), umma_desc_kmajor(k_addr + off), idesc_qk, kk > 0);
         }
+        umma_commit(k_empty + (i % kTcKStages));
         umma_commit(s_full + (i & 1));
       };
       mbar_wait(q_full, 0, p.st);
@@ -143,54 +153,53 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       for (int i = 0; i < ntiles; ++i) {
         if (i + 1 < ntiles) {
           const int n = i + 1;
-          mbar_wait(k_full + (n % kTcStages), (n / kTcStages) & 1, p.st);
-          if (n >= 2) mbar_wait(s_empty + (n & 1), ((n >> 1) - 1) & 1, p.st);
+          mbar_wait(k_full + (n % kTcKStages), (n / kTcKStages) & 1, p.st);
           tc_fence_after_sync();
           issue_qk(n);
         }
         mbar_wait(p_full, i & 1, p.st);
-        mbar_wait(v_full + (i % kTcStages), (i / kTcStages) & 1, p.st);
+        mbar_wait(v_full + (i % kTcVStages), (i / kTcVStages) & 1, p.st);
         tc_fence_after_sync();
-        const uint32_t v_addr = smem_u32(v_sm + (i % kTcStages) * KV_BYTES);
+        const uint32_t v_addr = smem_u32(v_sm + (i % kTcVStages) * KV_BYTES);
+        const uint32_t p_tmem = tmem + (uint32_t)((i & 1) * kTcKeyTile);  // P overwrote the first 64 columns of this S buffer
 #pragma unroll
-        for (int kk = 0; kk < kTcKeyTile / 16; ++kk) {
-          const uint32_t a_off = (kk >> 2) * PANEL_BYTES + (kk & 3) * 32;
-          umma_ss(tmem + 256, umma_desc_kmajor(p_addr + a_off), umma_desc_mnmajor(v_addr + kk * 2048, PANEL_BYTES), idesc_pv,
-                  i > 0 || kk > 0);
-        }
-        umma_commit(kv_empty + (i % kTcStages));
+        for (int kk = 0; kk < kTcKeyTile / 16; ++kk)
+          umma_ts(tmem + 256, p_tmem + kk * 8, umma_desc_mnmajor(v_addr + kk * 2048, PANEL_BYTES), idesc_pv, i > 0 || kk > 0);
+        umma_commit(v_empty + (i % kTcVStages));
         umma_commit(pv_done);
       }
     }
   } else {
-    // ===================== softmax: thread r owns row r =====================
-    const int row = threadIdx.x;
+    // ===================== softmax: two threads per row, 64 key columns each =====================
+    const int half = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
     const int tpos = q0 + (row >> p.logG);
     const int head = h * p.G + (row & (p.G - 1));
     const bool valid = tpos < Lq;
     const int nvis = valid ? visible_keys_tc(tpos, Lk, p.window, p.stride, p.causal) : 0;
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-    float m_ref = -INFINITY, l = 0.f;
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    float m_ref = -INFINITY, l = 0.f;  // l: sum over this thread's columns only
     for (int i = 0; i < ntiles; ++i) {
       const int bsel = i & 1;
       mbar_wait(s_full + bsel, (i >> 1) & 1, p.st);
       tc_fence_after_sync();
-      uint32_t su[kTcKeyTile / 32][32];
-#pragma unroll
-      for (int c = 0; c < kTcKeyTile / 32; ++c) tmem_ld32(lane_base + bsel * kTcKeyTile + c * 32, su[c]);
+      uint32_t su[2][32];
+      tmem_ld32(lane_base + bsel * kTcKeyTile + half * 64, su[0]);
+      tmem_ld32(lane_base + bsel * kTcKeyTile + half * 64 + 32, su[1]);
       tmem_ld_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_empty + bsel);
-
-      const int lim = nvis - i * kTcKeyTile;
-      float mt = -INFINITY;
+      const int lim = nvis - i * kTcKeyTile - half * 64;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int j = 0; j < kTcKeyTile; ++j) {
+      for (int j = 0; j < 64; ++j) {
         const float v = (j < lim) ? __uint_as_float(su[j >> 5][j & 31]) * p.scale2 : -INFINITY;
         su[j >> 5][j & 31] = __float_as_uint(v);
-        mt = fmaxf(mt, v);
+        mx4[j & 3] = fmaxf(mx4[j & 3], v);
       }
+      float mt = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // the row maximum needs the other half: exchange through shared memory (buffers alternate per tile)
+      xch[bsel * 256 + half * 128 + row] = mt;
+      asm volatile("bar.sync 1, 256;\n" ::: "memory");
+      mt = fmaxf(mt, xch[bsel * 256 + (half ^ 1) * 128 + row]);
       const bool need = mt > m_ref + 8.f;
       float factor = 1.f;
       if (need) {
@@ -198,57 +207,55 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         m_ref = mt;
         l *= factor;
       }
-      if (i > 0) {
-        mbar_wait(pv_done, (i - 1) & 1, p.st);  // P V of the previous tile is complete: O is stable, the P tile is free
+      if (i > 0 && __any_sync(0xffffffffu, need)) {
+        mbar_wait(pv_done, (i - 1) & 1, p.st);  // P V of the previous tile is complete: O is stable
         tc_fence_after_sync();
-        if (__any_sync(0xffffffffu, need)) {
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld32(lane_base + 256 + c * 32, r);
-            tmem_ld_wait();
+        for (int c = 0; c < D / 64; ++c) {
+          uint32_t r[32];
+          tmem_ld32(lane_base + 256 + half * (D / 2) + c * 32, r);
+          tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * factor);
-            tmem_st32(lane_base + 256 + c * 32, r);
-          }
-          tmem_st_wait();
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * factor);
+          tmem_st32(lane_base + 256 + half * (D / 2) + c * 32, r);
         }
+        tmem_st_wait();
       }
       const float msafe = (m_ref == -INFINITY) ? 0.f : m_ref;
-      const uint32_t prow = smem_u32(p_sm) + row * 128;
-      float lsum = 0.f;
+      // P as 16-bit pairs goes back into tensor memory over this thread's share of the tile's logits (keys
+      // 64*half .. 64*half+63 -> packed columns 32*half .. 32*half+31), where the P V product reads its A operand
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t pk[32];
 #pragma unroll
-      for (int c = 0; c < kTcKeyTile / 8; ++c) {  // 16-byte chunks of 8 keys
-        float pv[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          pv[j] = fast_exp2(__uint_as_float(su[(c * 8 + j) >> 5][(c * 8 + j) & 31]) - msafe);
-          lsum += pv[j];
-        }
-        const uint32_t addr = prow + (c >> 3) * PANEL_BYTES + (((c & 7) ^ (row & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(DT<T>::pack(pv[0], pv[1])),
-                     "r"(DT<T>::pack(pv[2], pv[3])), "r"(DT<T>::pack(pv[4], pv[5])), "r"(DT<T>::pack(pv[6], pv[7]))
-                     : "memory");
+      for (int j = 0; j < 32; ++j) {
+        const float p0 = fast_exp2(__uint_as_float(su[(2 * j) >> 5][(2 * j) & 31]) - msafe);
+        const float p1 = fast_exp2(__uint_as_float(su[(2 * j + 1) >> 5][(2 * j + 1) & 31]) - msafe);
+        ls[j & 3] += p0 + p1;
+        pk[j] = DT<T>::pack(p0, p1);
       }
-      l += lsum;
-      fence_proxy_async();
+      tmem_st32(lane_base + bsel * kTcKeyTile + half * 32, pk);
+      tmem_st_wait();
+      l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
     }
-    // ---- epilogue: O / l ----
+    // ---- epilogue: O / l (the row sum is the sum of the two halves) ----
     if (ntiles > 0) {
       mbar_wait(pv_done, (ntiles - 1) & 1, p.st);
       tc_fence_after_sync();
     }
+    xch[(ntiles & 1) * 256 + half * 128 + row] = l;
+    asm volatile("bar.sync 1, 256;\n" ::: "memory");
+    l += xch[(ntiles & 1) * 256 + (half ^ 1) * 128 + row];
     const float inv = l > 0.f ? 1.f / l : 0.f;
-    if (valid) p.lse[(long long)(qs + tpos) * p.Hq + head] = l > 0.f ? m_ref + log2f(l) : -INFINITY;
-    T* orow = static_cast<T*>(p.o) + (long long)(qs + tpos) * p.o_sn + (long long)head * p.o_sh;
+    if (valid && half == 0) p.lse[(long long)(qs + tpos) * p.Hq + head] = l > 0.f ? m_ref + log2f(l) : -INFINITY;
+    T* orow = static_cast<T*>(p.o) + (long long)(qs + tpos) * p.o_sn + (long long)head * p.o_sh + half * (D / 2);
 #pragma unroll
-    for (int c = 0; c < D / 32; ++c) {
+    for (int c = 0; c < D / 64; ++c) {
       uint32_t r[32];
       if (ntiles > 0) {
-        tmem_ld32(lane_base + 256 + c * 32, r);
+        tmem_ld32(lane_base + 256 + half * (D / 2) + c * 32, r);
         tmem_ld_wait();
       } else {
 #pragma unroll
@@ -269,7 +276,7 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem, 512);
+  if (warp == 9) tmem_dealloc(tmem, 512);
 }
 
 template <typename T, int D>
@@ -284,12 +291,12 @@ static int launch_dense_fwd_tc(const void* q, const void* k, const void* v, cons
   if (rc) return rc;
   rc = make_tmap_3d(&tmV, DT<T>::kTmapType, v, D, p.Hkv, Nk, S[5], S[4], 64, 1, kTcKeyTile);
   if (rc) return rc;
-  const size_t smem = 1024 + 128 * D * 2 + 2 * kTcStages * kTcKeyTile * D * 2 + 128 * kTcKeyTile * 2 + 32 * sizeof(uint64_t);
+  const size_t smem = 1024 + 128 * D * 2 + (kTcKStages + kTcVStages) * kTcKeyTile * D * 2 + 32 * sizeof(uint64_t) + 512 * sizeof(float);
   auto kern = dense_fwd_tc_kernel<T, D>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_rc(e);
   dim3 grid((max_seqlen_q + QT - 1) / QT, p.B, p.Hkv);
-  { LaunchScope ls_("dense_fwd_tc", stream); kern<<<grid, 192, smem, stream>>>(tmQ, tmK, tmV, p); }
+  { LaunchScope ls_("dense_fwd_tc", stream); kern<<<grid, 320, smem, stream>>>(tmQ, tmK, tmV, p); }
   return cuda_rc(cudaGetLastError());
 }
 
