@@ -24,6 +24,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+os.environ["NCCL_DEBUG"] = os.environ.get("NSA_BENCH_NCCL_DEBUG", "WARN")  # keep NCCL's banner off stdout: one JSON line only
+
 import torch  # noqa: E402
 
 # ----------------------------------------------------------------------------------------------------
@@ -90,7 +92,7 @@ class ClockSampler:
         self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         try:
             self.p = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                       "-lms", "200"], stdout=self.f, stderr=subprocess.DEVNULL)
+                                       "-lms", "50"], stdout=self.f, stderr=subprocess.DEVNULL)
         except OSError:
             self.p = None
 
@@ -199,17 +201,84 @@ def kernel_work(name, f):
         "linear_dw": ("tensor", lin_f / 2),
         "linear_dx": ("tensor", lin_f / 2),
     }
+    name = name[:-3] if name.endswith("_tc") else name   # tcgen05 variants do the same algorithmic work
     return table.get(name)
+
+
+def decode_microbench(ops, dev):
+    """The three single-token operators on (a) the bandwidth-sized case of the reference's decode self-tests
+    (batch 76, cache 8192, 32q/4kv heads, d=128, block 64, top-16, ragged lengths) and (b) the shapes of the
+    generation config (batch 4, 8192-token context, 32q/2kv heads).  Returns microseconds and achieved GB/s on the
+    ALGORITHMIC bytes (K and V rows that must be read, 2 bytes each)."""
+    out = {}
+    for tag, B, L, Hq, Hkv in (("bandwidth_case", 76, 8192, 32, 4), ("generation_case", 4, 8192 + 128, 32, 2)):
+        g = torch.Generator().manual_seed(42)
+        d, bs, T, ks, st = 128, 64, 16 if tag == "bandwidth_case" else 8, 32, 16
+        if tag == "bandwidth_case":
+            seqlens = torch.clamp(torch.arange(B, dtype=torch.int32) * 128 + 1, max=L)
+            seqlens = seqlens[torch.randperm(B, generator=g)]
+        else:
+            seqlens = torch.full((B,), 8192 + 64, dtype=torch.int32)
+        q = torch.randn(B, Hq, d, generator=g).to(torch.bfloat16).to(dev)
+        k = torch.randn(B, L, Hkv, d, generator=g).to(torch.bfloat16).to(dev)
+        v = torch.randn(B, L, Hkv, d, generator=g).to(torch.bfloat16).to(dev)
+        Lc = (L - ks) // st + 1
+        ck, cv = k[:, :Lc].contiguous(), v[:, :Lc].contiguous()
+        clen = torch.clamp((seqlens - ks) // st + 1, min=0).to(torch.int32)
+        sl, cl = seqlens.to(dev), clen.to(dev)
+        nb = (seqlens.long() - 1) // bs + 1
+        idx = torch.full((Hkv, B, T), -1, dtype=torch.int32)
+        for b in range(B):
+            n = int(nb[b])
+            for h in range(Hkv):
+                pick = torch.randperm(n, generator=g)[: min(T, n)].sort().values
+                idx[h, b, : pick.numel()] = pick.int()
+        idx = idx.to(dev)
+        sel_rows = sum(min(bs, int(seqlens[b]) - int(i) * bs) for b in range(B) for h in range(1) for i in idx[0, b].tolist() if i >= 0)
+        work = {
+            "flash_attention_decode": (lambda: ops.flash_attention_decode(q, k, v, sl), 4 * int(seqlens.sum()) * Hkv * d),
+            "topk_sparse_attention_decode": (lambda: ops.topk_sparse_attention_decode(q, k, v, idx, bs, sl), 4 * sel_rows * Hkv * d),
+            "compressed_attention_decode": (lambda: ops.compressed_attention_decode(q, ck, cv, sl, cl, ks, st, bs, T),
+                                            4 * int(clen.sum()) * Hkv * d),
+        }
+        flush = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.float32, device=dev)
+        res = {}
+        import native_sparse_attention_triton_b200 as pkg
+        for name, (fn, nbytes) in work.items():
+            for _ in range(3):
+                fn()
+            times = []
+            pkg._lib.profile_collect()
+            pkg._lib.profile(True)
+            reps = 10
+            for _ in range(reps):
+                flush.zero_()   # 256 MB write: evicts the caches between timed calls
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                times.append(e0.elapsed_time(e1))
+            kern = pkg._lib.profile_collect()   # device time of the library's kernels alone (CUDA events around each launch)
+            pkg._lib.profile(False)
+            kernel_ms = sum(v[1] for v in kern.values()) / reps
+            times.sort()
+            ms = times[len(times) // 2]
+            res[name] = dict(op_us=ms * 1e3, kernel_us=kernel_ms * 1e3, algorithmic_bytes=nbytes,
+                             kernel_gb_per_s=nbytes / 1e9 / (kernel_ms / 1e3), kernels=sorted(kern))
+        out[tag] = res
+    return out
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=None, help="override the sequence length (parity/debug only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode-operator micro-benchmark")
     args = ap.parse_args()
     if args.tokens:
         WORKLOAD["tokens"] = args.tokens
@@ -300,6 +369,11 @@ def main():
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     e2e_ms = float(e2e_t.item())
     status = pkg.device_status()
+    decode = None
+    if rank == 0 and not args.no_decode:
+        del t, host
+        torch.cuda.empty_cache()
+        decode = decode_microbench(ops, dev)
 
     if rank != 0:
         if dist is not None:
@@ -335,7 +409,8 @@ def main():
                 e2e=dict(value=e2e_ms, unit="ms", h2d_bytes_per_step=h2d_bytes, d2h_bytes_per_step=4),
                 gpu_launches=launches, roofline=roofline, cpu_baseline=cpu,
                 tokens_per_s=world * N / (ms / 1e3), useful_tflops_per_gpu=useful_tflops,
-                frac_of_tc_peak=useful_tflops / pk["tc_sustained"], per_kernel_ms=per_kernel, device_status=status)
+                frac_of_tc_peak=useful_tflops / pk["tc_sustained"], per_kernel_ms=per_kernel, decode=decode,
+                hbm_peak_gb_per_s=pk["hbm"], device_status=status)
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()

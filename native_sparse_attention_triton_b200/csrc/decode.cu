@@ -147,24 +147,36 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
 }
 
 // out[b, h*G + g, :] = sum_s o_s * 2^(m_s - m*) / sum_s l_s * 2^(m_s - m*)
+// One CTA per (sequence, KV head, query head of the group), one thread per output column; the split weights are
+// computed once by the first warp and shared.
 template <typename T>
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, void* o,
                                       long long o_sb, long long o_sh, int Hkv, int G, int S, int D) {
-  const int bh = blockIdx.x, b = bh / Hkv, h = bh % Hkv;
-  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
-    const int g = idx / D, c = idx % D;
-    float mstar = -INFINITY;
-    for (int s = 0; s < S; ++s) mstar = fmaxf(mstar, part_ml[((size_t)(bh * S + s) * 16 + g) * 2]);
-    float num = 0.f, den = 0.f;
-    if (mstar != -INFINITY) {
-      for (int s = 0; s < S; ++s) {
-        const float* ml = part_ml + ((size_t)(bh * S + s) * 16 + g) * 2;
-        const float wgt = fast_exp2(ml[0] - mstar);
-        den += ml[1] * wgt;
-        num += part_o[((size_t)(bh * S + s) * 16 + g) * D + c] * wgt;
-      }
-    }
-    static_cast<T*>(o)[(long long)b * o_sb + (long long)(h * G + g) * o_sh + c] = DT<T>::from_float(den > 0.f ? num / den : 0.f);
+  __shared__ float w_sh[64];
+  __shared__ float inv_den;
+  const int g = blockIdx.x % G;
+  const int bh = blockIdx.x / G, b = bh / Hkv, h = bh % Hkv;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    if (lane < S) { const float* ml = part_ml + ((size_t)(bh * S + lane) * 16 + g) * 2; m0 = ml[0]; l0 = ml[1]; }
+    if (lane + 32 < S) { const float* ml = part_ml + ((size_t)(bh * S + lane + 32) * 16 + g) * 2; m1 = ml[0]; l1 = ml[1]; }
+    float mstar = fmaxf(m0, m1);
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) mstar = fmaxf(mstar, __shfl_xor_sync(0xffffffffu, mstar, off));
+    const float w0 = (m0 == -INFINITY) ? 0.f : fast_exp2(m0 - mstar), w1 = (m1 == -INFINITY) ? 0.f : fast_exp2(m1 - mstar);
+    float den = l0 * w0 + l1 * w1;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) den += __shfl_xor_sync(0xffffffffu, den, off);
+    w_sh[lane] = w0;
+    w_sh[lane + 32] = w1;
+    if (lane == 0) inv_den = den > 0.f ? 1.f / den : 0.f;
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    float num = 0.f;
+    for (int s = 0; s < S; ++s) num += part_o[((size_t)(bh * S + s) * 16 + g) * D + c] * w_sh[s];
+    static_cast<T*>(o)[(long long)b * o_sb + (long long)(h * G + g) * o_sh + c] = DT<T>::from_float(num * inv_den);
   }
 }
 
@@ -187,7 +199,7 @@ static int launch_decode(const void* k, const void* v, const long long* kv_strid
   const int tasks = p.B * p.Hkv * p.S;
   { LaunchScope ls_("decode_attn", stream); kern<<<(tasks + WARPS - 1) / WARPS, WARPS * 32, smem, stream>>>(tmK, tmV, p); }
   if (p.S > 1)
-    { LaunchScope ls_("decode_combine", stream); decode_combine_kernel<T><<<p.B * p.Hkv, 256, 0, stream>>>(p.part_o, p.part_ml, p.o, p.o_sb, p.o_sh, p.Hkv, p.G, p.S, D); }
+    { LaunchScope ls_("decode_combine", stream); decode_combine_kernel<T><<<p.B * p.Hkv * p.G, 128, 0, stream>>>(p.part_o, p.part_ml, p.o, p.o_sb, p.o_sh, p.Hkv, p.G, p.S, D); }
   return cuda_rc(cudaGetLastError());
 }
 
@@ -426,6 +438,7 @@ extern "C" int nsa_flash_attn_decode(const void* q, const void* k, const void* v
   p.B = batch; p.Hq = num_q_heads; p.Hkv = num_kv_heads; p.G = num_q_heads / num_kv_heads; p.T = 0; p.block_size = kKeyTile;
   const int max_tiles = (cache_len + kKeyTile - 1) / kKeyTile;
   p.S = num_splits < 1 ? 1 : (num_splits > max_tiles ? max_tiles : num_splits);
+  if (p.S > 64) p.S = 64;  // the combine kernel handles at most 64 partial results per row
   p.tiles_per_split = (max_tiles + p.S - 1) / p.S;
   const long long need = p.S > 1 ? (long long)batch * num_kv_heads * p.S * 16 * (head_dim + 2) : 0;
   if (need > 0 && (!scratch || scratch_floats < need)) return kWorkspace;
@@ -455,6 +468,7 @@ extern "C" int nsa_topk_sparse_attn_decode(const void* q, const void* k, const v
   p.B = batch; p.Hq = num_q_heads; p.Hkv = num_kv_heads; p.G = num_q_heads / num_kv_heads; p.T = topk; p.block_size = block_size;
   const int max_tiles = topk * (block_size / kKeyTile);
   p.S = num_splits < 1 ? 1 : (num_splits > max_tiles ? max_tiles : num_splits);
+  if (p.S > 64) p.S = 64;  // the combine kernel handles at most 64 partial results per row
   p.tiles_per_split = (max_tiles + p.S - 1) / p.S;
   const long long need = p.S > 1 ? (long long)batch * num_kv_heads * p.S * 16 * (head_dim + 2) : 0;
   if (need > 0 && (!scratch || scratch_floats < need)) return kWorkspace;
