@@ -653,6 +653,12 @@ static bool legacy_mma() {
   return v;
 }
 
+// NSA_B200_DKDV_ROWS_AS_M=1 selects the earlier tcgen05 dK/dV kernel (64-key tiles, token rows as M) for the dense pass
+static bool dkdv_rows_as_m() {
+  static const bool v = [] { const char* e = getenv("NSA_B200_DKDV_ROWS_AS_M"); return e && e[0] == '1'; }();
+  return v;
+}
+
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 template <typename T, int D, bool SPARSE>
@@ -749,8 +755,12 @@ static int run_dense_bwd(const void* q, const void* k, const void* v, const void
   dim3 grid((max_k + kKeyTile - 1) / kKeyTile, (max_q + chunk - 1) / chunk, batch * Hkv);
   int rc;
   if constexpr (D == 128) {
-    rc = (G >= 4 && !legacy_mma()) ? launch_dkdv_tc<T, false>(q, dout, k, v, ds, total_q, total_k, grid, d, stream)
-                                   : launch_dkdv<T, D, false>(q, dout, k, v, ds, total_q, total_k, grid, d, stream);
+    if (legacy_mma())
+      rc = launch_dkdv<T, D, false>(q, dout, k, v, ds, total_q, total_k, grid, d, stream);
+    else if (dkdv_rows_as_m() && G >= 4)
+      rc = launch_dkdv_tc<T, false>(q, dout, k, v, ds, total_q, total_k, grid, d, stream);
+    else
+      rc = launch_dense_dkdv_tc<T>(q, dout, k, v, ds, total_q, total_k, max_q, max_k, batch, d, stream);
   } else {
     rc = launch_dkdv<T, D, false>(q, dout, k, v, ds, total_q, total_k, grid, d, stream);
   }

@@ -52,4 +52,10 @@ template <typename T, bool SPARSE>
 int launch_dkdv_tc(const void* q, const void* dout, const void* k, const void* v, const long long* strides, int Nq, int Nk,
                    dim3 grid, DkdvParams p, cudaStream_t stream);
 
+// tcgen05 dK/dV pass of the dense attention with the keys as the M dimension (dense_dkdv_tc.cu); head_dim 128,
+// group size a power of two <= 16.  p.chunk = tokens per CTA (a multiple of 128).
+template <typename T>
+int launch_dense_dkdv_tc(const void* q, const void* dout, const void* k, const void* v, const long long* strides, int Nq, int Nk,
+                         int max_q, int max_k, int batch, DkdvParams p, cudaStream_t stream);
+
 }  // namespace nsa

@@ -20,6 +20,7 @@ namespace nsa {
 enum : int {
   kErrWaitTimeout = 1,   // a bounded mbarrier wait gave up
   kErrBadIndex = 2,      // an index read from memory was outside its legal range
+  kErrSmemLayout = 4,    // the dynamic shared-memory base is not aligned as the kernel's tile layout needs
 };
 
 struct Status {
