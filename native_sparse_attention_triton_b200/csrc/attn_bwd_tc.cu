@@ -221,27 +221,33 @@ dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // Two independent streams of work share the tensor pipe: S/dP of tile ns (needs the tile's rows and a free TMEM
       // buffer) and dV/dK of tile nd (needs P and dS of that tile).  Whichever is ready is issued; neither blocks the other.
       int ns = 0, nd = 0;
-      long long t0 = clock64();
+      long long t0 = 0;
+      int idle = 0;
       while (nd < ntiles) {
         bool progressed = false;
-        if (ns < ntiles && ns - nd < 2 && mbar_try_wait(row_full + (ns % kRowStages), (ns / kRowStages) & 1) &&
-            (ns < 2 || mbar_try_wait(sdp_empty + (ns & 1), ((ns >> 1) - 1) & 1))) {
+        if (ns < ntiles && ns - nd < 2 && mbar_test(row_full + (ns % kRowStages), (ns / kRowStages) & 1) &&
+            (ns < 2 || mbar_test(sdp_empty + (ns & 1), ((ns >> 1) - 1) & 1))) {
           tc_fence_after_sync();
           issue_sdp(ns);
           ++ns;
           progressed = true;
         }
-        if (nd < ns && mbar_try_wait(pds_full, nd & 1)) {
+        if (nd < ns && mbar_test(pds_full, nd & 1)) {
           tc_fence_after_sync();
           issue_dvdk(nd);
           ++nd;
           progressed = true;
         }
         if (progressed) {
-          t0 = clock64();
-        } else if (clock64() - t0 > (1ll << 30) || (p.st.word && (*reinterpret_cast<volatile int*>(p.st.word) & kErrWaitTimeout))) {
-          p.st.raise(kErrWaitTimeout);  // bounded: give up instead of spinning forever
-          break;
+          idle = 0;
+        } else if (((++idle) & 1023) == 0) {
+          // bounded: every 1024 idle polls look at the clock and at the grid-wide abort flag (a global-memory read,
+          // far too slow to sit in the polling path itself)
+          if (idle == 1024) t0 = clock64();
+          if (clock64() - t0 > (1ll << 30) || (p.st.word && (*reinterpret_cast<volatile int*>(p.st.word) & kErrWaitTimeout))) {
+            p.st.raise(kErrWaitTimeout);
+            break;
+          }
         }
       }
       umma_commit(all_done);

@@ -162,6 +162,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking test of a phase: unlike try_wait, which may suspend the thread for a system-dependent time when the phase
+// is not complete, this returns at once.  For threads that poll several barriers and must not sleep on one of them.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+
 // Bounded wait: gives up after ~2^30 SM clocks (about half a second), raising kErrWaitTimeout.
 // Once any thread of the grid has given up, every later wait returns at once, so a broken
 // pipeline costs one timeout in total, not one per wait.  Returns false on timeout; the caller

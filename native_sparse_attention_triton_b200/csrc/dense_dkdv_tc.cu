@@ -20,7 +20,6 @@
 #include "tc5.cuh"
 
 namespace nsa {
-
 namespace {
 constexpr int kQStages = 3;
 constexpr int kDoStages = 2;
@@ -163,68 +162,71 @@ dense_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
   } else if (warp == 9) {
     // ===================== MMA issuer =====================
-    if (lane == 0) {
+    // The whole warp runs the control flow (so that it stays warp-uniform and cheap); one elected lane issues.
+    {
       const uint32_t idesc_s = umma_idesc<T>(128, 128, false, false);
       const uint32_t idesc_t = umma_idesc<T>(128, 128, false, true);
-      const uint32_t k_addr = smem_u32(k_sm), v_addr = smem_u32(v_sm);
-      const uint32_t q_base = smem_u32(q_ring), do_base = smem_u32(do_ring);
-      auto issue_logits = [&](uint32_t a_addr, uint32_t b_addr, uint32_t d_col) {
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
-          umma_ss(tmem + d_col, umma_desc_kmajor(a_addr + off), umma_desc_kmajor(b_addr + off), idesc_s, kk > 0);
+      const uint32_t k_addr = smem_u32(k_sm), v_addr = smem_u32(v_sm), q_base = smem_u32(q_ring), do_base = smem_u32(do_ring);
+      auto issue_logits = [&](uint32_t a_addr, uint32_t b_addr, uint32_t d_tmem, uint64_t* bar) {
+        if (elect_one()) {
+          umma_block_ss<D / 16, kPanelBytes>(d_tmem, a_addr, b_addr, idesc_s);
+          umma_commit(bar);
         }
+        __syncwarp();
       };
-      // the 16 rows of reduction step kk sit in packed columns 64*(kk/4) + 8*(kk%4) of the A region
-      auto issue_grad = [&](uint32_t a_col, uint32_t b_addr, uint32_t d_col, bool first) {
-#pragma unroll
-        for (int kk = 0; kk < 128 / 16; ++kk)
-          umma_ts(tmem + d_col, tmem + a_col + 64 * (kk >> 2) + 8 * (kk & 3), umma_desc_mnmajor(b_addr + kk * 2048, kPanelBytes),
-                  idesc_t, !first || kk > 0);
+      auto issue_grad = [&](uint32_t a_tmem, uint32_t b_addr, uint32_t d_tmem, bool first, uint64_t* bar) {
+        if (elect_one()) {
+          umma_block_ts<128 / 16, kPanelBytes>(d_tmem, a_tmem, b_addr, idesc_t, !first);
+          umma_commit(bar);
+        }
+        __syncwarp();
       };
       mbar_wait(kv_full, 0, p.st);
       // Four queues share the tensor pipe.  S(i) may start once dV(i-1) has been issued (it overwrites P^T(i-1);
       // the pipe executes in issue order), dP(i) once dK(i-1) has been issued; dV(i) needs P^T(i), dK(i) needs dS^T(i).
       int ns = 0, np = 0, nv = 0, nk = 0;
-      long long t0 = clock64();
+      long long t0 = 0;
+      int idle = 0;
       while (nk < ntiles) {
         bool progressed = false;
-        if (nv < ns && nv < np && mbar_try_wait(p_full, nv & 1)) {
+        if (nv < ns && nv < np && mbar_test(p_full, nv & 1)) {
           tc_fence_after_sync();
-          issue_grad(256, do_base + (nv % kDoStages) * kTileBytes, 0, nv == 0);
-          umma_commit(do_empty + (nv % kDoStages));
+          issue_grad(tmem + 256, do_base + (nv % kDoStages) * kTileBytes, tmem, nv == 0, do_empty + (nv % kDoStages));
           ++nv;
           progressed = true;
         }
-        if (ns < ntiles && ns == nv && mbar_try_wait(q_full + (ns % kQStages), (ns / kQStages) & 1)) {
+        if (ns < ntiles && ns == nv && mbar_test(q_full + (ns % kQStages), (ns / kQStages) & 1)) {
           tc_fence_after_sync();
-          issue_logits(k_addr, q_base + (ns % kQStages) * kTileBytes, 256);
-          umma_commit(s_full);
+          issue_logits(k_addr, q_base + (ns % kQStages) * kTileBytes, tmem + 256, s_full);
           ++ns;
           progressed = true;
         }
-        if (nk < np && mbar_try_wait(ds_full, nk & 1)) {
+        if (nk < np && mbar_test(ds_full, nk & 1)) {
           tc_fence_after_sync();
-          issue_grad(384, q_base + (nk % kQStages) * kTileBytes, 128, nk == 0);
-          umma_commit(q_empty + (nk % kQStages));
+          issue_grad(tmem + 384, q_base + (nk % kQStages) * kTileBytes, tmem + 128, nk == 0, q_empty + (nk % kQStages));
           ++nk;
           progressed = true;
         }
-        if (np < ntiles && np == nk && mbar_try_wait(do_full + (np % kDoStages), (np / kDoStages) & 1)) {
+        if (np < ntiles && np == nk && mbar_test(do_full + (np % kDoStages), (np / kDoStages) & 1)) {
           tc_fence_after_sync();
-          issue_logits(v_addr, do_base + (np % kDoStages) * kTileBytes, 384);
-          umma_commit(dp_full);
+          issue_logits(v_addr, do_base + (np % kDoStages) * kTileBytes, tmem + 384, dp_full);
           ++np;
           progressed = true;
         }
         if (progressed) {
-          t0 = clock64();
-        } else if (clock64() - t0 > (1ll << 30) || (p.st.word && (*reinterpret_cast<volatile int*>(p.st.word) & kErrWaitTimeout))) {
-          p.st.raise(kErrWaitTimeout);  // bounded: give up instead of spinning forever
-          break;
+          idle = 0;
+        } else if (((++idle) & 1023) == 0) {
+          // bounded: every 1024 idle polls look at the clock and at the grid-wide abort flag (a global-memory read,
+          // far too slow to sit in the polling path itself)
+          if (idle == 1024) t0 = clock64();
+          if (clock64() - t0 > (1ll << 30) || (p.st.word && (*reinterpret_cast<volatile int*>(p.st.word) & kErrWaitTimeout))) {
+            p.st.raise(kErrWaitTimeout);
+            break;
+          }
         }
       }
-      umma_commit(all_done);
+      if (elect_one()) umma_commit(all_done);
+      __syncwarp();
     }
   } else {
     // ===================== softmax / dS threads: thread = (key, half of the row columns) =====================

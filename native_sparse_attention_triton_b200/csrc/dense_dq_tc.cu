@@ -1,15 +1,18 @@
 // dQ pass of dense strided-causal attention on the 5th-generation tensor cores.
 //
 // CTA = 128 rows = (128/G tokens) x (G heads of one KV head), key tiles of 128:
-//     S  = Q  K^T   [128 x 128]  A = Q  (K-major), B = K tile (K-major)       TMEM [0,128)
-//     dP = dO V^T   [128 x 128]  A = dO (K-major), B = V tile (K-major)       TMEM [128,256)
-//     dQ += dS K    [128 x D]    A = dS (SMEM, K-major), B = K tile (MN-major) TMEM [256,256+D)
-// Q and dO stay in SMEM for the whole CTA; K tiles alternate between two buffers (a K tile is needed from its
-// S product until its dQ product), V has one buffer (free as soon as dP is done).  The issuing thread keeps two
-// independent streams going -- S/dP of the next tile and dQ of the current one -- whichever is ready.
-//   warps 0..7 : two threads per row (64 key columns each): P = exp2(S*scale - lse), dS = P (dP - delta) scale
-//                as 16-bit into the SMEM tile the dQ product reads; they also compute delta = sum(O * dO) of their
-//                row up front and publish (lse, delta) for the dK/dV pass; at the end they store dQ
+//     S  = Q  K^T   [128 x 128]  A = Q  (SMEM, K-major), B = K tile (SMEM, K-major)       TMEM [0,128)
+//     dP = dO V^T   [128 x 128]  A = dO (SMEM, K-major), B = V tile (SMEM, K-major)       TMEM [128,256)
+//     dQ += dS K    [128 x D]    A = dS (TMEM, 16-bit),  B = K tile (SMEM, MN-major)      TMEM [256,256+D)
+// Q and dO stay in SMEM for the whole CTA; K tiles go through a ring of three (a K tile lives from its S product
+// to its dQ product), V tiles through a ring of two.  dS is written by the softmax threads over the dP logits it
+// was computed from, so the dQ product reads its A operand from tensor memory.  The issuing thread polls three
+// queues; the pipe order in steady state is S(i+1), dQ(i), dP(i+1): the S product of the next tile covers the
+// dS phase of the current one and dQ/dP cover the P phase of the next.
+//   warps 0..7 : two threads per row (64 key columns each).  P phase (after S): P = exp2(S*scale - lse) kept in
+//                registers; dS phase (after dP): dS = P (dP - delta) scale -> TMEM.  They also compute
+//                delta = sum(O * dO) of their row up front and publish (lse, delta) for the dK/dV pass; at the end
+//                they store dQ
 //   warp 8     : TMA producer;   warp 9 : TMEM allocation and MMA issue (one thread)
 #include "attn_bwd.h"
 #include "attn_tile.cuh"
@@ -19,6 +22,11 @@
 
 namespace nsa {
 
+namespace {
+constexpr int kDqKStages = 3;
+constexpr int kDqVStages = 2;
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(320, 1)
 dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
@@ -27,29 +35,30 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   constexpr int PANELS = D / 64;
   constexpr int PANEL_BYTES = 128 * 128;
   constexpr int ROW_BYTES = 128 * D * 2;   // Q, dO, K tile, V tile: all [128][D]
-  constexpr int DS_BYTES = 128 * KT * 2;   // dS tile [128 rows][128 keys]: 2 panels
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* q_sm = smem;
   uint8_t* do_sm = q_sm + ROW_BYTES;
-  uint8_t* k_sm = do_sm + ROW_BYTES;        // two buffers
-  uint8_t* v_sm = k_sm + 2 * ROW_BYTES;
-  uint8_t* ds_sm = v_sm + ROW_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ds_sm + DS_BYTES);
+  uint8_t* k_sm = do_sm + ROW_BYTES;                 // ring of kDqKStages
+  uint8_t* v_sm = k_sm + kDqKStages * ROW_BYTES;     // ring of kDqVStages
+  float* delta_sh = reinterpret_cast<float*>(v_sm + kDqVStages * ROW_BYTES);  // [2][128] partial row sums of O*dO
+  uint64_t* bars = reinterpret_cast<uint64_t*>(delta_sh + 256);
   uint64_t* qdo_full = bars;
-  uint64_t* k_full = bars + 1;      // [2]
-  uint64_t* k_empty = k_full + 2;   // [2]
-  uint64_t* v_full = k_empty + 2;
-  uint64_t* v_empty = v_full + 1;
-  uint64_t* sdp_full = v_empty + 1;
-  uint64_t* sdp_empty = sdp_full + 1;
-  uint64_t* ds_full = sdp_empty + 1;
-  uint64_t* ds_empty = ds_full + 1;
-  uint64_t* all_done = ds_empty + 1;
+  uint64_t* k_full = bars + 1;
+  uint64_t* k_empty = k_full + kDqKStages;
+  uint64_t* v_full = k_empty + kDqKStages;
+  uint64_t* v_empty = v_full + kDqVStages;
+  uint64_t* s_full = v_empty + kDqVStages;
+  uint64_t* s_empty = s_full + 1;
+  uint64_t* dp_full = s_empty + 1;
+  uint64_t* ds_full = dp_full + 1;
+  uint64_t* all_done = ds_full + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(all_done + 1);
-  float* delta_sh = reinterpret_cast<float*>(tmem_slot + 2);  // [2][128] partial row sums of O*dO
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (smem_u32(smem) & 1023u) {  // the swizzled operand tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) p.st.raise(kErrSmemLayout);
+    return;
+  }
   const int b = blockIdx.y, h = blockIdx.z;
   const int qs = __ldg(p.cu_q + b), Lq = __ldg(p.cu_q + b + 1) - qs;
   const int ksq = __ldg(p.cu_k + b), Lk = __ldg(p.cu_k + b + 1) - ksq;
@@ -66,16 +75,18 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kDqKStages; ++s) {
       mbar_init(k_full + s, 1);
       mbar_init(k_empty + s, 1);
     }
-    mbar_init(v_full, 1);
-    mbar_init(v_empty, 1);
-    mbar_init(sdp_full, 1);
-    mbar_init(sdp_empty, 8);
+    for (int s = 0; s < kDqVStages; ++s) {
+      mbar_init(v_full + s, 1);
+      mbar_init(v_empty + s, 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(s_empty, 8);
+    mbar_init(dp_full, 1);
     mbar_init(ds_full, 8);
-    mbar_init(ds_empty, 1);
     mbar_init(all_done, 1);
     fence_barrier_init();
   }
@@ -98,76 +109,82 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tma_load_3d(do_sm + pn * PANEL_BYTES, &tmDO, qdo_full, pn * 64, h * p.G, qs + q0);
       }
       for (int i = 0; i < ntiles; ++i) {
-        const int s = i & 1;
-        if (i >= 2) mbar_wait(k_empty + s, ((i >> 1) - 1) & 1, p.st);
-        mbar_expect_tx(k_full + s, ROW_BYTES);
+        const int sk = i % kDqKStages, sv = i % kDqVStages;
+        if (i >= kDqKStages) mbar_wait(k_empty + sk, ((i / kDqKStages) - 1) & 1, p.st);
+        mbar_expect_tx(k_full + sk, ROW_BYTES);
 #pragma unroll
         for (int pn = 0; pn < PANELS; ++pn)
-          tma_load_3d(k_sm + s * ROW_BYTES + pn * PANEL_BYTES, &tmK, k_full + s, pn * 64, h, ksq + i * KT);
-        if (i >= 1) mbar_wait(v_empty, (i - 1) & 1, p.st);
-        mbar_expect_tx(v_full, ROW_BYTES);
+          tma_load_3d(k_sm + sk * ROW_BYTES + pn * PANEL_BYTES, &tmK, k_full + sk, pn * 64, h, ksq + i * KT);
+        if (i >= kDqVStages) mbar_wait(v_empty + sv, ((i / kDqVStages) - 1) & 1, p.st);
+        mbar_expect_tx(v_full + sv, ROW_BYTES);
 #pragma unroll
-        for (int pn = 0; pn < PANELS; ++pn) tma_load_3d(v_sm + pn * PANEL_BYTES, &tmV, v_full, pn * 64, h, ksq + i * KT);
+        for (int pn = 0; pn < PANELS; ++pn)
+          tma_load_3d(v_sm + sv * ROW_BYTES + pn * PANEL_BYTES, &tmV, v_full + sv, pn * 64, h, ksq + i * KT);
       }
     }
   } else if (warp == 9) {
     // ===================== MMA issuer =====================
-    if (lane == 0 && ntiles > 0) {
+    // The whole warp runs the control flow converged; one elected lane issues (see tc5.cuh on why).
+    if (ntiles > 0) {
       const uint32_t idesc_s = umma_idesc<T>(128, KT, false, false);
       const uint32_t idesc_q = umma_idesc<T>(128, D, false, true);
-      const uint32_t q_addr = smem_u32(q_sm), do_addr = smem_u32(do_sm), v_addr = smem_u32(v_sm), ds_addr = smem_u32(ds_sm);
-      auto issue_sdp = [&](int i) {
-        const uint32_t k_addr = smem_u32(k_sm + (i & 1) * ROW_BYTES);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * PANEL_BYTES + (kk & 3) * 32;
-          umma_ss(tmem, umma_desc_kmajor(q_addr + off), umma_desc_kmajor(k_addr + off), idesc_s, kk > 0);
-        }
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * PANEL_BYTES + (kk & 3) * 32;
-          umma_ss(tmem + 128, umma_desc_kmajor(do_addr + off), umma_desc_kmajor(v_addr + off), idesc_s, kk > 0);
-        }
-        umma_commit(v_empty);
-        umma_commit(sdp_full);
-      };
-      auto issue_dq = [&](int i) {
-        const uint32_t k_addr = smem_u32(k_sm + (i & 1) * ROW_BYTES);
-#pragma unroll
-        for (int kk = 0; kk < KT / 16; ++kk) {
-          const uint32_t a_off = (kk >> 2) * PANEL_BYTES + (kk & 3) * 32;
-          umma_ss(tmem + 256, umma_desc_kmajor(ds_addr + a_off), umma_desc_mnmajor(k_addr + kk * 2048, PANEL_BYTES), idesc_q,
-                  i > 0 || kk > 0);
-        }
-        umma_commit(k_empty + (i & 1));
-        umma_commit(ds_empty);
-      };
+      const uint32_t q_addr = smem_u32(q_sm), do_addr = smem_u32(do_sm), k_base = smem_u32(k_sm), v_base = smem_u32(v_sm);
       mbar_wait(qdo_full, 0, p.st);
-      int ns = 0, nd = 0;
-      long long t0 = clock64();
-      while (nd < ntiles) {
+      // S(i) may start once the softmax threads have read S(i-1); dP(i) once dQ(i-1) has been issued (it overwrites
+      // dS(i-1); the pipe executes in issue order); dQ(i) needs dS(i).
+      int ns = 0, np = 0, nq = 0;
+      long long t0 = 0;
+      int idle = 0;
+      while (nq < ntiles) {
         bool progressed = false;
-        if (ns < ntiles && ns - nd < 2 && mbar_try_wait(k_full + (ns & 1), (ns >> 1) & 1) && mbar_try_wait(v_full, ns & 1) &&
-            (ns < 1 || mbar_try_wait(sdp_empty, (ns - 1) & 1))) {
+        if (ns < ntiles && mbar_test(k_full + (ns % kDqKStages), (ns / kDqKStages) & 1) &&
+            (ns < 1 || mbar_test(s_empty, (ns - 1) & 1))) {
           tc_fence_after_sync();
-          issue_sdp(ns);
+          if (elect_one()) {
+            umma_block_ss<D / 16, PANEL_BYTES>(tmem, q_addr, k_base + (ns % kDqKStages) * ROW_BYTES, idesc_s);
+            umma_commit(s_full);
+          }
+          __syncwarp();
           ++ns;
           progressed = true;
         }
-        if (nd < ns && mbar_try_wait(ds_full, nd & 1)) {
+        if (nq < np && mbar_test(ds_full, nq & 1)) {
           tc_fence_after_sync();
-          issue_dq(nd);
-          ++nd;
+          const int sk = nq % kDqKStages;
+          if (elect_one()) {
+            umma_block_ts<KT / 16, PANEL_BYTES>(tmem + 256, tmem + 128, k_base + sk * ROW_BYTES, idesc_q, nq > 0);
+            umma_commit(k_empty + sk);
+          }
+          __syncwarp();
+          ++nq;
+          progressed = true;
+        }
+        if (np < ntiles && np == nq && np < ns && mbar_test(v_full + (np % kDqVStages), (np / kDqVStages) & 1)) {
+          tc_fence_after_sync();
+          const int sv = np % kDqVStages;
+          if (elect_one()) {
+            umma_block_ss<D / 16, PANEL_BYTES>(tmem + 128, do_addr, v_base + sv * ROW_BYTES, idesc_s);
+            umma_commit(v_empty + sv);
+            umma_commit(dp_full);
+          }
+          __syncwarp();
+          ++np;
           progressed = true;
         }
         if (progressed) {
-          t0 = clock64();
-        } else if (clock64() - t0 > (1ll << 30) || (p.st.word && (*reinterpret_cast<volatile int*>(p.st.word) & kErrWaitTimeout))) {
-          p.st.raise(kErrWaitTimeout);
-          break;
+          idle = 0;
+        } else if (((++idle) & 1023) == 0) {
+          // bounded: every 1024 idle polls look at the clock and at the grid-wide abort flag (a global-memory read,
+          // far too slow to sit in the polling path itself)
+          if (idle == 1024) t0 = clock64();
+          if (clock64() - t0 > (1ll << 30) || (p.st.word && (*reinterpret_cast<volatile int*>(p.st.word) & kErrWaitTimeout))) {
+            p.st.raise(kErrWaitTimeout);
+            break;
+          }
         }
       }
-      umma_commit(all_done);
+      if (elect_one()) umma_commit(all_done);
+      __syncwarp();
     }
   } else {
     // ===================== softmax / dS: two threads per row =====================
@@ -200,36 +217,43 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const float lse2 = valid ? __ldg(p.lse + (long long)(qs + tpos) * p.Hq + head) : INFINITY;
     if (valid && half == 0) p.ld[(long long)(qs + tpos) * p.Hq + head] = make_float2(lse2, delta);
     const float nlse = -lse2;
+    const float ndsc = -delta * p.sm_scale;
 
     for (int i = 0; i < ntiles; ++i) {
-      mbar_wait(sdp_full, i & 1, p.st);
+      // ---- P phase ----
+      mbar_wait(s_full, i & 1, p.st);
       tc_fence_after_sync();
-      uint32_t su[2][32], du[2][32];
-      tmem_ld32(lane_base + half * 64, su[0]);
-      tmem_ld32(lane_base + half * 64 + 32, su[1]);
-      tmem_ld32(lane_base + 128 + half * 64, du[0]);
-      tmem_ld32(lane_base + 128 + half * 64 + 32, du[1]);
-      tmem_ld_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(sdp_empty);
-      const int lim = nvis - i * KT - half * 64;
-      uint32_t dw[32];
+      float pf[64];
+      {
+        uint32_t su[2][32];
+        tmem_ld32(lane_base + half * 64, su[0]);
+        tmem_ld32(lane_base + half * 64 + 32, su[1]);
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_empty);
+        const int lim = nvis - i * KT - half * 64;
 #pragma unroll
-      for (int j = 0; j < 64; j += 2) {
-        const float p0 = masked_exp2(j < lim, fmaf(__uint_as_float(su[j >> 5][j & 31]), p.scale2, nlse));
-        const float p1 = masked_exp2(j + 1 < lim, fmaf(__uint_as_float(su[(j + 1) >> 5][(j + 1) & 31]), p.scale2, nlse));
-        const float d0 = p0 * (__uint_as_float(du[j >> 5][j & 31]) - delta) * p.sm_scale;
-        const float d1 = p1 * (__uint_as_float(du[(j + 1) >> 5][(j + 1) & 31]) - delta) * p.sm_scale;
-        dw[j >> 1] = DT<T>::pack(d0, d1);
+        for (int j = 0; j < 64; ++j) pf[j] = masked_exp2(j < lim, fmaf(__uint_as_float(su[j >> 5][j & 31]), p.scale2, nlse));
       }
-      if (i > 0) mbar_wait(ds_empty, (i - 1) & 1, p.st);  // dQ of the previous tile has read the dS tile
-      const uint32_t dsrow = smem_u32(ds_sm) + half * PANEL_BYTES + row * 128;
+      // ---- dS phase ----
+      mbar_wait(dp_full, i & 1, p.st);
+      tc_fence_after_sync();
+      {
+        uint32_t du[2][32];
+        tmem_ld32(lane_base + 128 + half * 64, du[0]);
+        tmem_ld32(lane_base + 128 + half * 64 + 32, du[1]);
+        tmem_ld_wait();
+        uint32_t dw[32];
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(dsrow + ((c ^ (row & 7)) << 4)), "r"(dw[c * 4]),
-                     "r"(dw[c * 4 + 1]), "r"(dw[c * 4 + 2]), "r"(dw[c * 4 + 3]) : "memory");
-      fence_proxy_async();
+        for (int j = 0; j < 64; j += 2) {
+          const float d0 = pf[j] * fmaf(__uint_as_float(du[j >> 5][j & 31]), p.sm_scale, ndsc);
+          const float d1 = pf[j + 1] * fmaf(__uint_as_float(du[(j + 1) >> 5][(j + 1) & 31]), p.sm_scale, ndsc);
+          dw[j >> 1] = DT<T>::pack(d0, d1);
+        }
+        tmem_st32(lane_base + 128 + half * 64, dw);  // over this thread's own dP logits
+        tmem_st_wait();
+      }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(ds_full);
@@ -281,7 +305,7 @@ static int launch_dense_dq_tc(const void* k, const void* v, long long k_sn, long
   if (rc) return rc;
   rc = make_tmap_3d(&tmV, DT<T>::kTmapType, v, D, p.Hkv, total_k, v_sh, v_sn, 64, 1, 128);
   if (rc) return rc;
-  const size_t smem = 1024 + 5 * (128 * D * 2) + 128 * 128 * 2 + 16 * sizeof(uint64_t) + 16 + 256 * sizeof(float);
+  const size_t smem = (size_t)(2 + kDqKStages + kDqVStages) * (128 * D * 2) + 256 * sizeof(float) + 24 * sizeof(uint64_t) + 16;
   auto kern = dense_dq_tc_kernel<T, D>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_rc(e);

@@ -21,6 +21,15 @@ __device__ __forceinline__ uint64_t umma_desc_mnmajor(uint32_t saddr, uint32_t p
          ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 
+// Moves the start address of a descriptor by `bytes` (a multiple of 16).  The start-address field is the low 14 bits in
+// units of 16 bytes; shared memory is smaller than 256 KB, so the sum never carries out of the field and one 32-bit add
+// on the low word is enough.  The issuing thread builds each descriptor once and advances it per MMA: it has a budget of
+// only a few dozen issue slots per MMA before it, not the tensor pipe, becomes the limit.
+__device__ __forceinline__ uint64_t umma_desc_advance(uint64_t desc, uint32_t bytes) {
+  const uint32_t lo = static_cast<uint32_t>(desc) + (bytes >> 4);
+  return (desc & 0xFFFFFFFF00000000ull) | lo;
+}
+
 // ---- instruction descriptor: fp32 accumulate, 16-bit inputs ----
 template <typename T>
 __device__ __forceinline__ constexpr uint32_t umma_idesc(int M, int N, bool a_mn_major, bool b_mn_major) {
@@ -48,6 +57,33 @@ __device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
       ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(acc)
       : "memory");
+}
+
+// ---- blocks of MMAs over the reduction dimension ----
+// How to issue (measured on B200 with blocks of 8 MMAs of 128x128x16, a commit and a barrier test between blocks):
+// the queue in front of the tensor pipe is shallow, so every instruction the issuing thread executes between two MMAs
+// is time the pipe waits.  The whole warp must run the control flow CONVERGED, with only the MMA and commit
+// instructions under elect_one(), and descriptors must be built from (warp-uniform) addresses at each use: the
+// compiler then keeps all of that arithmetic in the uniform datapath and the block runs at 64 clocks per MMA, the pipe's
+// rate.  The same code inside `if (lane == 0)` takes 91 clocks per MMA.
+// D = A B^T, both operands K-major SMEM tiles made of [rows][64-element] panels PANEL bytes apart; NK steps of 16.
+template <int NK, int PANEL>
+__device__ __forceinline__ void umma_block_ss(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t idesc) {
+#pragma unroll
+  for (int kk = 0; kk < NK; ++kk) {
+    const uint32_t off = (kk >> 2) * PANEL + (kk & 3) * 32;
+    umma_ss(d_tmem, umma_desc_kmajor(a_addr + off), umma_desc_kmajor(b_addr + off), idesc, kk > 0);
+  }
+}
+// D (+)= A B with A in TMEM as 16-bit pairs written by threads that own 64 source columns each (reduction step kk
+// sits at column 64*(kk/4) + 8*(kk%4) of the A region) and B an MN-major SMEM tile (16 reduction rows = 2048 bytes,
+// 64-element panels PANEL bytes apart).
+template <int NK, int PANEL>
+__device__ __forceinline__ void umma_block_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, uint32_t idesc, bool accumulate) {
+  umma_ts(d_tmem, a_tmem, umma_desc_mnmajor(b_addr, PANEL), idesc, accumulate);
+#pragma unroll
+  for (int kk = 1; kk < NK; ++kk)
+    umma_ts(d_tmem, a_tmem + 64 * (kk >> 2) + 8 * (kk & 3), umma_desc_mnmajor(b_addr + kk * 2048, PANEL), idesc, true);
 }
 
 // the mbarrier gets one arrival when every MMA issued so far by this thread has completed
