@@ -15,6 +15,7 @@
 //               share a key tile are added with fp32 red.global into a zeroed accumulator and
 //               converted to the storage type at the end.
 #include <cstdlib>
+#include <utility>
 
 #include "attn_tile.cuh"
 #include "dispatch.h"
@@ -332,13 +333,17 @@ struct IndexParams {
   const int* topk_idx;
   const int* cu_seqlens;
   const int* cu_blocks;  // [B+1] prefix sum of ceil(len / block_size)
-  int* count;            // [Hkv * TB]
-  int* cursor;           // [Hkv * TB]
-  int* offsets;          // [Hkv * TB + 1] exclusive scan of count
-  int* item_base;        // [Hkv * TB + 1] exclusive scan of ceil(count / chunk)
+  // A bin is (kv head, token window, global block): bin = (head * NW + window) * TB + block.  Binning the tokens of a
+  // block's list by window, with the window as the slower index, makes CTAs that run at the same time gather Q/dO rows
+  // of the same few thousand tokens, so the rows are read from DRAM once and then served by L2.
+  int* count;            // [bins]
+  int* cursor;           // [bins]
+  int* offsets;          // [bins + 1] exclusive scan of count
+  int* item_base;        // [bins + 1] exclusive scan of ceil(count / chunk)
   int* list;             // [capacity] global token ids
   long long t_sh, t_sn, t_sk;
   int N, B, Hkv, T, block_size, TB, chunk;
+  int W, NW;             // tokens per window, windows
   long long capacity;
   Status st;
 };
@@ -357,7 +362,7 @@ __global__ void index_scatter_kernel(IndexParams p) {
   for (int j = 0; j < p.T; ++j) {
     const int idx = __ldg(tptr + j * p.t_sk);
     if (idx < 0 || idx > bq) continue;
-    const int x = h * p.TB + blk0 + idx;
+    const int x = (h * p.NW + n / p.W) * p.TB + blk0 + idx;
     if (blk0 + idx >= p.TB) { p.st.raise(kErrBadIndex); continue; }
     if (!FILL) {
       atomicAdd(p.count + x, 1);
@@ -373,7 +378,7 @@ __global__ void index_scatter_kernel(IndexParams p) {
 __global__ void index_scan_kernel(IndexParams p) {
   __shared__ int s_cnt[1024], s_itm[1024];
   __shared__ int carry_cnt, carry_itm;
-  const int total = p.Hkv * p.TB;
+  const int total = p.Hkv * p.NW * p.TB;
   if (threadIdx.x == 0) { carry_cnt = 0; carry_itm = 0; }
   __syncthreads();
   for (int base = 0; base < total; base += 1024) {
@@ -433,7 +438,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
   int tok_begin, tok_count;             // dense: first token position and count; sparse: list offset and count
   if (SPARSE) {
     const int item = blockIdx.x;
-    const int total_x = p.Hkv * p.TB;
+    const int total_x = p.Hkv * p.NW * p.TB;
     if (item >= __ldg(p.item_base + total_x)) return;
     int lo = 0, hi = total_x;  // item_base[lo] <= item < item_base[hi]
     while (hi - lo > 1) {
@@ -441,7 +446,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       if (__ldg(p.item_base + mid) <= item) lo = mid; else hi = mid;
     }
     const int x = lo;
-    h = x / p.TB;
+    h = x / (p.NW * p.TB);
     const int gb = x % p.TB;
     const int b = find_sequence(p.cu_blocks, p.B, gb);
     qs = __ldg(p.cu_q + b);
@@ -653,12 +658,6 @@ static bool legacy_mma() {
   return v;
 }
 
-// NSA_B200_DKDV_ROWS_AS_M=1 selects the earlier tcgen05 dK/dV kernel (64-key tiles, token rows as M) for the dense pass
-static bool dkdv_rows_as_m() {
-  static const bool v = [] { const char* e = getenv("NSA_B200_DKDV_ROWS_AS_M"); return e && e[0] == '1'; }();
-  return v;
-}
-
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 template <typename T, int D, bool SPARSE>
@@ -745,7 +744,7 @@ static int run_dense_bwd(const void* q, const void* k, const void* v, const void
   DkdvParams d;
   d.ld = ld; d.dk32 = dk32; d.dv32 = dv32; d.cu_q = cu_q; d.cu_k = cu_k;
   d.cu_blocks = nullptr; d.offsets = nullptr; d.item_base = nullptr; d.list = nullptr;
-  d.B = batch; d.Hq = Hq; d.Hkv = Hkv; d.G = G; d.TB = 0; d.block_size = kKeyTile;
+  d.B = batch; d.Hq = Hq; d.Hkv = Hkv; d.G = G; d.TB = 0; d.NW = 1; d.block_size = kKeyTile;
   int chunk = 256;
   while (chunk < 1024 && chunk * 16 < max_q) chunk <<= 1;
   d.chunk = chunk;
@@ -757,8 +756,6 @@ static int run_dense_bwd(const void* q, const void* k, const void* v, const void
   if constexpr (D == 128) {
     if (legacy_mma())
       rc = launch_dkdv<T, D, false>(q, dout, k, v, ds, total_q, total_k, grid, d, stream);
-    else if (dkdv_rows_as_m() && G >= 4)
-      rc = launch_dkdv_tc<T, false>(q, dout, k, v, ds, total_q, total_k, grid, d, stream);
     else
       rc = launch_dense_dkdv_tc<T>(q, dout, k, v, ds, total_q, total_k, max_q, max_k, batch, d, stream);
   } else {
@@ -773,9 +770,18 @@ static int run_dense_bwd(const void* q, const void* k, const void* v, const void
 
 constexpr int kSparseChunk = 512;  // tokens of one block's list handled by one CTA
 
+// Token windows of the inverted index: as many tokens as keep the Q and dO rows of one KV-head group (G heads) within
+// about half of the L2 cache, a power of two, at least 1024.  Returns (tokens per window, windows).
+static std::pair<int, int> sparse_windows(int N, int G, int D) {
+  const long long bytes_per_token = 2ll * G * D * 2;
+  int W = 1024;
+  while (2ll * W * bytes_per_token <= (64ll << 20)) W <<= 1;
+  return {W, (N + W - 1) / W};
+}
+
 static size_t sparse_ws_bytes(int N, int batch, int Hq, int Hkv, int D, int topk, int block_size) {
   const size_t TB = (size_t)N / block_size + batch;
-  const size_t x = (size_t)Hkv * TB + 1;
+  const size_t x = (size_t)Hkv * sparse_windows(N, Hq / Hkv, D).second * TB + 1;
   return align_up((size_t)N * Hq * sizeof(float2), 256) + 2 * align_up((size_t)N * Hkv * D * sizeof(float), 256) +
          4 * align_up(x * sizeof(int), 256) + align_up((size_t)Hkv * N * topk * sizeof(int), 256);
 }
@@ -788,7 +794,8 @@ static int run_sparse_bwd(const void* q, const void* k, const void* v, const voi
   // S: q_n q_h k_n k_h v_n v_h o_n o_h do_n do_h dq_n dq_h dk_n dk_h dv_n dv_h idx_h idx_n idx_k
   const int G = Hq / Hkv;
   const int TB = N / block_size + batch;
-  const size_t X = (size_t)Hkv * TB + 1;
+  const auto [W, NW] = sparse_windows(N, G, D);
+  const size_t X = (size_t)Hkv * NW * TB + 1;
   uint8_t* w = static_cast<uint8_t*>(ws);
   float2* ld = reinterpret_cast<float2*>(w);
   w += align_up((size_t)N * Hq * sizeof(float2), 256);
@@ -821,7 +828,7 @@ static int run_sparse_bwd(const void* q, const void* k, const void* v, const voi
   ip.topk_idx = topk_idx; ip.cu_seqlens = cu; ip.cu_blocks = cu_blocks; ip.count = count; ip.cursor = cursor;
   ip.offsets = offsets; ip.item_base = item_base; ip.list = list;
   ip.t_sh = S[16]; ip.t_sn = S[17]; ip.t_sk = S[18];
-  ip.N = N; ip.B = batch; ip.Hkv = Hkv; ip.T = topk; ip.block_size = block_size; ip.TB = TB; ip.chunk = kSparseChunk;
+  ip.N = N; ip.B = batch; ip.Hkv = Hkv; ip.T = topk; ip.block_size = block_size; ip.TB = TB; ip.chunk = kSparseChunk; ip.W = W; ip.NW = NW;
   ip.capacity = (long long)Hkv * N * topk;
   ip.st = p.st;
   const long long hn = (long long)Hkv * N;
@@ -848,16 +855,16 @@ static int run_sparse_bwd(const void* q, const void* k, const void* v, const voi
   DkdvParams d;
   d.ld = ld; d.dk32 = dk32; d.dv32 = dv32; d.cu_q = cu; d.cu_k = cu;
   d.cu_blocks = cu_blocks; d.offsets = offsets; d.item_base = item_base; d.list = list;
-  d.B = batch; d.Hq = Hq; d.Hkv = Hkv; d.G = G; d.TB = TB; d.chunk = kSparseChunk; d.block_size = block_size;
+  d.B = batch; d.Hq = Hq; d.Hkv = Hkv; d.G = G; d.TB = TB; d.NW = NW; d.chunk = kSparseChunk; d.block_size = block_size;
   d.window = 1; d.stride = 1; d.causal = 1;
   d.scale2 = p.scale2; d.sm_scale = sm_scale; d.st = p.st;
   const long long ds[8] = {S[0], S[1], S[2], S[3], S[4], S[5], S[8], S[9]};
   // upper bound on work items: every selection in a full chunk, plus one partial chunk per (head, block)
-  const long long max_items = ((long long)Hkv * N * topk) / kSparseChunk + (long long)Hkv * TB;
+  const long long max_items = ((long long)Hkv * N * topk) / kSparseChunk + (long long)Hkv * NW * TB;
   dim3 grid((unsigned)max_items, block_size / kKeyTile, 1);
   int rc;
   if constexpr (D == 128) {
-    rc = (G >= 4 && (G & (G - 1)) == 0 && !legacy_mma()) ? launch_dkdv_tc<T, true>(q, dout, k, v, ds, N, N, grid, d, stream)
+    rc = (G >= 4 && (G & (G - 1)) == 0 && !legacy_mma()) ? launch_sparse_dkdv_tc<T>(q, dout, k, v, ds, N, grid, d, stream)
                                                          : launch_dkdv<T, D, true>(q, dout, k, v, ds, N, N, grid, d, stream);
   } else {
     rc = launch_dkdv<T, D, true>(q, dout, k, v, ds, N, N, grid, d, stream);

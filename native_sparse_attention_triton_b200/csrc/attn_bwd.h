@@ -19,6 +19,8 @@ struct DkdvParams {
   const int* item_base;
   const int* list;
   int B, Hq, Hkv, G, TB, chunk, block_size;
+  int NW;  // sparse: token windows per KV head; bin x = (head * NW + window) * TB + block
+
   int window, stride, causal;
   float scale2, sm_scale;
   Status st;
@@ -46,11 +48,11 @@ struct DenseBwdParams {
 int dense_dq_tc(const void* k, const void* v, long long k_sn, long long k_sh, long long v_sn, long long v_sh, int total_q,
                 int total_k, int max_seqlen_q, int head_dim, int dtype, DenseBwdParams p, cudaStream_t stream);
 
-// tcgen05 implementation of the dK/dV pass (attn_bwd_tc.cu); head_dim 128 only.
-// strides: q_n q_h k_n k_h v_n v_h do_n do_h (elements)
-template <typename T, bool SPARSE>
-int launch_dkdv_tc(const void* q, const void* dout, const void* k, const void* v, const long long* strides, int Nq, int Nk,
-                   dim3 grid, DkdvParams p, cudaStream_t stream);
+// tcgen05 dK/dV pass of the top-k sparse attention (sparse_dkdv_tc.cu); head_dim 128, group size a power of two.
+// strides: q_n q_h k_n k_h v_n v_h do_n do_h (elements); grid = (work items, 64-key tiles per block).
+template <typename T>
+int launch_sparse_dkdv_tc(const void* q, const void* dout, const void* k, const void* v, const long long* strides, int Nk, dim3 grid,
+                          DkdvParams p, cudaStream_t stream);
 
 // tcgen05 dK/dV pass of the dense attention with the keys as the M dimension (dense_dkdv_tc.cu); head_dim 128,
 // group size a power of two <= 16.  p.chunk = tokens per CTA (a multiple of 128).

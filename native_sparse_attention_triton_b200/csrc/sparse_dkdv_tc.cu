@@ -1,0 +1,411 @@
+// dK/dV pass of the top-k sparse attention on the 5th-generation tensor cores (head_dim 128).
+//
+// CTA = one tile of 64 keys of a selected block (K and V tile resident in SMEM) x a stream of row tiles taken from
+// the block's inverted index (the tokens that selected it); a row tile is 128 rows = (128/G tokens) x (G query
+// heads).  All four products have M = 128:
+//     S    = Q  K^T          [128 rows x 64 keys]   A = Q  (K-major),  B = K tile (K-major)
+//     dP   = dO V^T          [128 rows x 64 keys]   A = dO (K-major),  B = V tile (K-major)
+//     dV^T = dO^T P          [128 d    x 64 keys]   A = dO (MN-major), B = P  [rows][keys] (MN-major)
+//     dK^T = Q^T  dS         [128 d    x 64 keys]   A = Q  (MN-major), B = dS [rows][keys] (MN-major)
+// so the token/head rows are the reduction dimension of the last two and the G heads of a KV group are summed
+// inside the MMA.  S and dP are double-buffered in TMEM; dV^T and dK^T stay in TMEM for the whole CTA and are added
+// to the fp32 accumulators in global memory at the end.
+//
+// The rows of a tile are scattered tokens (4 KB of Q and of dO each).  One TMA box per token tops out near
+// 26 bytes/clock/SM (the box rate), so the rows are gathered with 16-byte cp.async instead (more than 60
+// bytes/clock/SM) by four loader warps, two per tile parity, into the same 128-byte-swizzled layout TMA would write.
+// The Q ring has three stages (a Q tile lives from its S product to its dK product), the dO ring two: dP(i) is
+// issued right behind S(i) and dV(i) as soon as P(i) is there, which needs only S(i), so dO(i) is released early.
+//   warps 0..7  : two threads per row (32 of the 64 key columns each).  P phase (after S): P = exp2(S*scale - lse)
+//                 -> 16-bit SMEM tile; dS phase (after dP): dS = P (dP - delta) scale -> SMEM tile.  The per-row
+//                 (lse, delta) come straight from global memory, fetched one tile ahead.  At the end they drain
+//                 dV / dK from TMEM
+//   warps 8..11 : cp.async loaders (warps 8,9: even tiles; 10,11: odd tiles)
+//   warp 12     : TMEM allocation, K/V TMA, MMA issue (converged warp, one elected lane issues)
+// TMEM columns: S0 [0,64) S1 [64,128) dP0 [128,192) dP1 [192,256) dV^T [256,320) dK^T [320,384).
+#include "attn_bwd.h"
+#include "host_util.h"
+#include "tc5.cuh"
+
+namespace nsa {
+
+namespace {
+constexpr int kSpQStages = 3;
+constexpr int kSpDoStages = 2;
+constexpr int kSpRowBytes = 128 * 128 * 2;  // Q or dO rows of one tile: 32 KB, 2 panels of [128 rows][64 d]
+constexpr int kSpRowPanel = 128 * 128;
+constexpr int kSpKvBytes = 64 * 128 * 2;    // K or V tile: 16 KB, 2 panels of [64 keys][64 d]
+constexpr int kSpKvPanel = 64 * 128;
+constexpr int kSpPdBytes = 128 * 64 * 2;    // P or dS tile [128 rows][64 keys]: one panel
+constexpr int kSpThreads = 13 * 32;
+}  // namespace
+
+template <typename T, int LOGG>
+__global__ void __launch_bounds__(kSpThreads, 1)
+sparse_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const T* __restrict__ q,
+                      const T* __restrict__ dout, long long q_sn, long long q_sh, long long do_sn, long long do_sh, DkdvParams p) {
+  constexpr int logG = LOGG;
+  constexpr int G = 1 << LOGG;
+  constexpr int D = 128;
+  constexpr int KT = 64;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* k_sm = smem;
+  uint8_t* v_sm = k_sm + kSpKvBytes;
+  uint8_t* p_sm = v_sm + kSpKvBytes;
+  uint8_t* ds_sm = p_sm + kSpPdBytes;
+  uint8_t* q_ring = ds_sm + kSpPdBytes;
+  uint8_t* do_ring = q_ring + kSpQStages * kSpRowBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(do_ring + kSpDoStages * kSpRowBytes);
+  uint64_t* kv_full = bars;
+  uint64_t* q_full = bars + 1;
+  uint64_t* q_empty = q_full + kSpQStages;
+  uint64_t* do_full = q_empty + kSpQStages;
+  uint64_t* do_empty = do_full + kSpDoStages;
+  uint64_t* s_full = do_empty + kSpDoStages;  // [2]
+  uint64_t* s_empty = s_full + 2;             // [2]
+  uint64_t* dp_full = s_empty + 2;            // [2]
+  uint64_t* dp_empty = dp_full + 2;           // [2]
+  uint64_t* p_full = dp_empty + 2;
+  uint64_t* p_empty = p_full + 1;
+  uint64_t* ds_full = p_empty + 1;
+  uint64_t* ds_empty = ds_full + 1;
+  uint64_t* all_done = ds_empty + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(all_done + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int TPT = 128 >> logG;  // tokens per row tile
+  if (smem_u32(smem) & 1023u) {  // the swizzled operand tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) p.st.raise(kErrSmemLayout);
+    return;
+  }
+
+  // ---- which key tile and which tokens ----
+  const int item = blockIdx.x;
+  const int total_x = p.Hkv * p.NW * p.TB;
+  if (item >= __ldg(p.item_base + total_x)) return;
+  int lo = 0, hi = total_x;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(p.item_base + mid) <= item) lo = mid; else hi = mid;
+  }
+  const int x = lo;
+  const int h = x / (p.NW * p.TB);
+  const int gb = x % p.TB;
+  const int b = find_sequence(p.cu_blocks, p.B, gb);
+  const int qs = __ldg(p.cu_q + b);
+  const int Lq = __ldg(p.cu_q + b + 1) - qs;
+  const int blk = gb - __ldg(p.cu_blocks + b);
+  const int kpos = blk * p.block_size + blockIdx.y * KT;
+  const int krow0 = qs + kpos;
+  const int kvalid = min(KT, Lq - kpos);
+  const int c = item - __ldg(p.item_base + x);
+  const int cnt = __ldg(p.offsets + x + 1) - __ldg(p.offsets + x);
+  const int tok_begin = __ldg(p.offsets + x) + c * p.chunk;
+  const int tok_count = min(p.chunk, cnt - c * p.chunk);
+  if (kvalid <= 0 || tok_count <= 0) return;
+  const int ntiles = (tok_count + TPT - 1) / TPT;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < kSpQStages; ++s) {
+      mbar_init(q_full + s, 64);
+      mbar_init(q_empty + s, 1);
+    }
+    for (int s = 0; s < kSpDoStages; ++s) {
+      mbar_init(do_full + s, 64);
+      mbar_init(do_empty + s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(s_full + s, 1);
+      mbar_init(s_empty + s, 8);
+      mbar_init(dp_full + s, 1);
+      mbar_init(dp_empty + s, 8);
+    }
+    mbar_init(p_full, 8);
+    mbar_init(p_empty, 1);
+    mbar_init(ds_full, 8);
+    mbar_init(ds_empty, 1);
+    mbar_init(all_done, 1);
+    fence_barrier_init();
+  }
+  if (warp == 12) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  if (warp >= 8 && warp < 12) {
+    // ===================== loaders: group 0 (warps 8,9) even tiles, group 1 (warps 10,11) odd tiles =====================
+    const int grp = (warp - 8) >> 1;
+    const int tl = threadIdx.x - (8 + 2 * grp) * 32;  // 0..63
+    const int chunk16 = tl & 15;                      // which 16 bytes of the row's 256
+    const int row_in_step = tl >> 4;                  // 4 rows per step
+    const uint32_t pn_off = (chunk16 >> 3) * kSpRowPanel;
+    const int c8 = chunk16 & 7;
+    // token ids of a tile: lane t of every loader warp holds the id of the tile's t-th token (at most 32 tokens per
+    // tile), fetched one round ahead so that the gather itself has no dependent global load in front of it
+    auto tile_tokens = [&](int i) {
+      const int ti = i * TPT + lane;
+      return (i < ntiles && lane < TPT && ti < tok_count) ? __ldg(p.list + tok_begin + ti) : -1;
+    };
+    const long long q_row0 = (long long)(h * p.G) * q_sh + chunk16 * 8, do_row0 = (long long)(h * p.G) * do_sh + chunk16 * 8;
+    int my_n = tile_tokens(grp);
+    for (int i = grp; i < ntiles; i += 2) {
+      const int next_n = tile_tokens(i + 2);
+      // Row r = slot * G + 4 * jj + row_in_step of the tile comes from token `slot`, head r % G.  Everything that does
+      // not depend on the token is folded into constants so that a copy costs a handful of instructions.
+      auto gather = [&](const T* src, long long sn, long long sh, long long row0, uint32_t dst_base) {
+        const uint32_t dst0 = dst_base + pn_off + row_in_step * 128;
+        const uint32_t sw0 = (uint32_t)((c8 ^ row_in_step) << 4), sw1 = (uint32_t)((c8 ^ (row_in_step + 4)) << 4);
+        const T* src0 = src + row0 + (long long)row_in_step * sh;
+#pragma unroll 4
+        for (int slot = 0; slot < (128 >> LOGG); ++slot) {
+          const int n = __shfl_sync(0xffffffffu, my_n, slot);
+          const bool ok = n >= 0;
+          const T* g = src0 + (long long)(ok ? n : 0) * sn;
+#pragma unroll
+          for (int jj = 0; jj < G / 4; ++jj) {
+            const int j = slot * (G / 4) + jj;  // r = 4 j + row_in_step; r & 7 = row_in_step + 4 (j & 1)
+            cp_async16(dst0 + j * 512 + ((j & 1) ? sw1 : sw0), g + (long long)(4 * jj) * sh, ok);  // missing tokens: zero fill
+          }
+        }
+      };
+      const int sq = i % kSpQStages, sd = i % kSpDoStages;
+      if (i >= kSpQStages) mbar_wait(q_empty + sq, ((i / kSpQStages) - 1) & 1, p.st);
+      gather(q, q_sn, q_sh, q_row0, smem_u32(q_ring + sq * kSpRowBytes));
+      cp_async_commit();
+      if (i >= kSpDoStages) mbar_wait(do_empty + sd, ((i / kSpDoStages) - 1) & 1, p.st);
+      gather(dout, do_sn, do_sh, do_row0, smem_u32(do_ring + sd * kSpRowBytes));
+      cp_async_commit();
+      cp_async_wait<1>();
+      fence_proxy_async();  // the tensor pipe reads these bytes through the async proxy
+      mbar_arrive(q_full + sq);
+      cp_async_wait<0>();
+      fence_proxy_async();
+      mbar_arrive(do_full + sd);
+      my_n = next_n;
+    }
+  } else if (warp == 12) {
+    // ===================== K/V load and MMA issue (converged warp, elected lane issues) =====================
+    if (elect_one()) {
+      mbar_expect_tx(kv_full, 2 * kSpKvBytes);
+#pragma unroll
+      for (int pn = 0; pn < 2; ++pn) {
+        tma_load_3d(k_sm + pn * kSpKvPanel, &tmK, kv_full, pn * 64, h, krow0);
+        tma_load_3d(v_sm + pn * kSpKvPanel, &tmV, kv_full, pn * 64, h, krow0);
+      }
+    }
+    __syncwarp();
+    const uint32_t idesc_s = umma_idesc<T>(128, KT, false, false);
+    const uint32_t idesc_t = umma_idesc<T>(128, KT, true, true);
+    const uint32_t k_addr = smem_u32(k_sm), v_addr = smem_u32(v_sm), p_addr = smem_u32(p_sm), ds_addr = smem_u32(ds_sm);
+    const uint32_t q_base = smem_u32(q_ring), do_base = smem_u32(do_ring);
+    // S/dP: A = rows (two [128][64] panels), B = K or V tile (two [64][64] panels)
+    auto issue_logits = [&](uint32_t a_addr, uint32_t b_addr, uint32_t d_tmem, uint64_t* bar) {
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_ss(d_tmem, umma_desc_kmajor(a_addr + (kk >> 2) * kSpRowPanel + (kk & 3) * 32),
+                  umma_desc_kmajor(b_addr + (kk >> 2) * kSpKvPanel + (kk & 3) * 32), idesc_s, kk > 0);
+        umma_commit(bar);
+      }
+      __syncwarp();
+    };
+    // dV^T/dK^T: reduction over the 128 rows, 16 at a time; A = rows MN-major (d as M), B = P or dS tile MN-major
+    auto issue_grad = [&](uint32_t a_addr, uint32_t b_addr, uint32_t d_tmem, bool first, uint64_t* bar_rows, uint64_t* bar_tile) {
+      if (elect_one()) {
+        umma_ss(d_tmem, umma_desc_mnmajor(a_addr, kSpRowPanel), umma_desc_mnmajor(b_addr, kSpPdBytes), idesc_t, !first);
+#pragma unroll
+        for (int kk = 1; kk < 128 / 16; ++kk)
+          umma_ss(d_tmem, umma_desc_mnmajor(a_addr + kk * 2048, kSpRowPanel), umma_desc_mnmajor(b_addr + kk * 2048, kSpPdBytes),
+                  idesc_t, true);
+        umma_commit(bar_rows);
+        umma_commit(bar_tile);
+      }
+      __syncwarp();
+    };
+    mbar_wait(kv_full, 0, p.st);
+    // Four queues share the tensor pipe: S(i) and dP(i) need their rows and a free TMEM buffer; dV(i) needs P(i) (and
+    // comes after dP(i), so that its completion can release the dO stage); dK(i) needs dS(i).
+    int ns = 0, np = 0, nv = 0, nk = 0;
+    long long t0 = 0;
+    int idle = 0;
+    while (nk < ntiles) {
+      bool progressed = false;
+      if (nv < np && mbar_test(p_full, nv & 1)) {
+        tc_fence_after_sync();
+        issue_grad(do_base + (nv % kSpDoStages) * kSpRowBytes, p_addr, tmem + 256, nv == 0, do_empty + (nv % kSpDoStages), p_empty);
+        ++nv;
+        progressed = true;
+      }
+      if (ns < ntiles && mbar_test(q_full + (ns % kSpQStages), (ns / kSpQStages) & 1) &&
+          (ns < 2 || mbar_test(s_empty + (ns & 1), ((ns >> 1) - 1) & 1))) {
+        tc_fence_after_sync();
+        issue_logits(q_base + (ns % kSpQStages) * kSpRowBytes, k_addr, tmem + (ns & 1) * KT, s_full + (ns & 1));
+        ++ns;
+        progressed = true;
+      }
+      if (nk < np && mbar_test(ds_full, nk & 1)) {
+        tc_fence_after_sync();
+        issue_grad(q_base + (nk % kSpQStages) * kSpRowBytes, ds_addr, tmem + 320, nk == 0, q_empty + (nk % kSpQStages), ds_empty);
+        ++nk;
+        progressed = true;
+      }
+      if (np < ns && mbar_test(do_full + (np % kSpDoStages), (np / kSpDoStages) & 1) &&
+          (np < 2 || mbar_test(dp_empty + (np & 1), ((np >> 1) - 1) & 1))) {
+        tc_fence_after_sync();
+        issue_logits(do_base + (np % kSpDoStages) * kSpRowBytes, v_addr, tmem + 128 + (np & 1) * KT, dp_full + (np & 1));
+        ++np;
+        progressed = true;
+      }
+      if (progressed) {
+        idle = 0;
+      } else if (((++idle) & 1023) == 0) {
+        // bounded: every 1024 idle polls look at the clock and at the grid-wide abort flag (a global-memory read,
+        // far too slow to sit in the polling path itself)
+        if (idle == 1024) t0 = clock64();
+        if (clock64() - t0 > (1ll << 30) || (p.st.word && (*reinterpret_cast<volatile int*>(p.st.word) & kErrWaitTimeout))) {
+          p.st.raise(kErrWaitTimeout);
+          break;
+        }
+      }
+    }
+    if (elect_one()) umma_commit(all_done);
+    __syncwarp();
+  } else {
+    // ===================== softmax / dS threads: two threads per row (32 of the 64 key columns each) =====================
+    const int half = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
+    const int slot = row >> logG;
+    const int head = h * p.G + (row & (p.G - 1));
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint32_t prow = smem_u32(p_sm) + row * 128, dsrow = smem_u32(ds_sm) + row * 128;
+    // per-row statistics are fetched ahead: the token of tile i+2, (lse, delta) of tile i+1
+    auto token_of = [&](int i) { return (i < ntiles && i * TPT + slot < tok_count) ? __ldg(p.list + tok_begin + i * TPT + slot) : -1; };
+    auto stats_of = [&](int n) { return n >= 0 ? __ldg(p.ld + (long long)n * p.Hq + head) : make_float2(INFINITY, 0.f); };
+    int n_cur = token_of(0), n_next = token_of(1);
+    float2 ld_cur = stats_of(n_cur);
+    for (int i = 0; i < ntiles; ++i) {
+      const int bsel = i & 1;
+      const int n_next2 = token_of(i + 2);
+      const float2 ld_next = stats_of(n_next);
+      // keys of this tile the row may see: those at or before its own position
+      int lim = n_cur >= 0 ? max(0, min(kvalid, (n_cur - qs) - kpos + 1)) : 0;
+      lim -= half * 32;  // relative to this thread's first column
+      const float nlse = -ld_cur.x, ndsc = -ld_cur.y * p.sm_scale;
+
+      // ---- P phase ----
+      mbar_wait(s_full + bsel, (i >> 1) & 1, p.st);
+      tc_fence_after_sync();
+      float pf[32];
+      {
+        uint32_t su[32];
+        tmem_ld32(lane_base + bsel * KT + half * 32, su);
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_empty + bsel);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) pf[j] = masked_exp2(j < lim, fmaf(__uint_as_float(su[j]), p.scale2, nlse));
+        uint32_t pw[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) pw[j] = DT<T>::pack(pf[2 * j], pf[2 * j + 1]);
+        if (i > 0) mbar_wait(p_empty, (i - 1) & 1, p.st);  // dV of the previous tile has read the P tile
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(prow + (((half * 4 + c4) ^ (row & 7)) << 4)), "r"(pw[c4 * 4]),
+                       "r"(pw[c4 * 4 + 1]), "r"(pw[c4 * 4 + 2]), "r"(pw[c4 * 4 + 3]) : "memory");
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+
+      // ---- dS phase ----
+      mbar_wait(dp_full + bsel, (i >> 1) & 1, p.st);
+      tc_fence_after_sync();
+      {
+        uint32_t du[32];
+        tmem_ld32(lane_base + 128 + bsel * KT + half * 32, du);
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dp_empty + bsel);
+        uint32_t dw[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const float d0 = pf[j] * fmaf(__uint_as_float(du[j]), p.sm_scale, ndsc);
+          const float d1 = pf[j + 1] * fmaf(__uint_as_float(du[j + 1]), p.sm_scale, ndsc);
+          dw[j >> 1] = DT<T>::pack(d0, d1);
+        }
+        if (i > 0) mbar_wait(ds_empty, (i - 1) & 1, p.st);  // dK of the previous tile has read the dS tile
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(dsrow + (((half * 4 + c4) ^ (row & 7)) << 4)), "r"(dw[c4 * 4]),
+                       "r"(dw[c4 * 4 + 1]), "r"(dw[c4 * 4 + 2]), "r"(dw[c4 * 4 + 3]) : "memory");
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_full);
+      n_cur = n_next;
+      n_next = n_next2;
+      ld_cur = ld_next;
+    }
+    // ---- drain: thread (d, half) holds column d of dV and dK for 32 of the 64 keys ----
+    mbar_wait(all_done, 0, p.st);
+    tc_fence_after_sync();
+    const int d = row;
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      float* dst = (which == 0 ? p.dv32 : p.dk32) + ((size_t)krow0 * p.Hkv + h) * D + d;
+      uint32_t r[32];
+      tmem_ld32(lane_base + 256 + which * 64 + half * 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int key = half * 32 + j;
+        if (key < kvalid) atomicAdd(dst + (size_t)key * p.Hkv * D, __uint_as_float(r[j]));
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 12) tmem_dealloc(tmem, 512);
+}
+
+template <typename T>
+int launch_sparse_dkdv_tc(const void* q, const void* dout, const void* k, const void* v, const long long* strides, int Nk, dim3 grid,
+                          DkdvParams p, cudaStream_t stream) {
+  constexpr int D = 128;
+  int logG = 0;
+  while ((1 << logG) < p.G) ++logG;
+  CUtensorMap tmK, tmV;
+  int rc = make_tmap_3d(&tmK, DT<T>::kTmapType, k, D, p.Hkv, Nk, strides[3], strides[2], 64, 1, 64);
+  if (rc) return rc;
+  rc = make_tmap_3d(&tmV, DT<T>::kTmapType, v, D, p.Hkv, Nk, strides[5], strides[4], 64, 1, 64);
+  if (rc) return rc;
+  const size_t smem = 2 * kSpKvBytes + 2 * kSpPdBytes + (kSpQStages + kSpDoStages) * kSpRowBytes + 32 * sizeof(uint64_t) + 16;
+  auto launch = [&](auto kern) -> int {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cuda_rc(e);
+    LaunchScope ls_("sparse_dkdv_tc", stream);
+    kern<<<grid, kSpThreads, smem, stream>>>(tmK, tmV, static_cast<const T*>(q), static_cast<const T*>(dout), strides[0], strides[1],
+                                             strides[6], strides[7], p);
+    return cuda_rc(cudaGetLastError());
+  };
+  switch (logG) {
+    case 2: return launch(sparse_dkdv_tc_kernel<T, 2>);
+    case 3: return launch(sparse_dkdv_tc_kernel<T, 3>);
+    case 4: return launch(sparse_dkdv_tc_kernel<T, 4>);
+    default: return kUnsupported;
+  }
+}
+
+template int launch_sparse_dkdv_tc<__nv_bfloat16>(const void*, const void*, const void*, const void*, const long long*, int, dim3,
+                                                  DkdvParams, cudaStream_t);
+template int launch_sparse_dkdv_tc<__half>(const void*, const void*, const void*, const void*, const long long*, int, dim3, DkdvParams,
+                                           cudaStream_t);
+
+}  // namespace nsa
