@@ -131,20 +131,20 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else if (warp == 9) {
     // ===================== MMA issuer =====================
-    if (lane == 0 && ntiles > 0) {
+    // The whole warp runs the control flow converged; one elected lane issues (see tc5.cuh on why).
+    if (ntiles > 0) {
       const uint32_t idesc_qk = umma_idesc<T>(128, kTcKeyTile, false, false);
       const uint32_t idesc_pv = umma_idesc<T>(128, D, false, true);
       const uint32_t q_addr = smem_u32(q_sm);
       auto issue_qk = [&](int i) {
         const uint32_t k_addr = smem_u32(k_sm + (i % kTcKStages) * KV_BYTES);
         const uint32_t d_tmem = tmem + (uint32_t)((i & 1) * kTcKeyTile);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * PANEL_BYTES + (kk & 3) * 32;
-          umma_ss(d_tmem, umma_desc_kmajor(q_addr + off), umma_desc_kmajor(k_addr + off), idesc_qk, kk > 0);
+        if (elect_one()) {
+          umma_block_ss<D / 16, PANEL_BYTES>(d_tmem, q_addr, k_addr, idesc_qk);
+          umma_commit(k_empty + (i % kTcKStages));
+          umma_commit(s_full + (i & 1));
         }
-        umma_commit(k_empty + (i % kTcKStages));
-        umma_commit(s_full + (i & 1));
+        __syncwarp();
       };
       mbar_wait(q_full, 0, p.st);
       mbar_wait(k_full, 0, p.st);
@@ -162,11 +162,14 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tc_fence_after_sync();
         const uint32_t v_addr = smem_u32(v_sm + (i % kTcVStages) * KV_BYTES);
         const uint32_t p_tmem = tmem + (uint32_t)((i & 1) * kTcKeyTile);  // P overwrote the first 64 columns of this S buffer
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < kTcKeyTile / 16; ++kk)
-          umma_ts(tmem + 256, p_tmem + kk * 8, umma_desc_mnmajor(v_addr + kk * 2048, PANEL_BYTES), idesc_pv, i > 0 || kk > 0);
-        umma_commit(v_empty + (i % kTcVStages));
-        umma_commit(pv_done);
+          for (int kk = 0; kk < kTcKeyTile / 16; ++kk)
+            umma_ts(tmem + 256, p_tmem + kk * 8, umma_desc_mnmajor(v_addr + kk * 2048, PANEL_BYTES), idesc_pv, i > 0 || kk > 0);
+          umma_commit(v_empty + (i % kTcVStages));
+          umma_commit(pv_done);
+        }
+        __syncwarp();
       }
     }
   } else {

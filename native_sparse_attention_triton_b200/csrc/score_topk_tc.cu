@@ -102,7 +102,8 @@ score_topk_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
     }
   } else if (warp == 9) {
-    if (lane == 0 && ntiles > 0) {
+    // The whole warp runs the control flow converged; one elected lane issues (see tc5.cuh on why).
+    if (ntiles > 0) {
       const uint32_t idesc = umma_idesc<T>(128, 128, false, false);
       const uint32_t q_addr = smem_u32(q_sm);
       mbar_wait(q_full, 0, p.st);
@@ -112,13 +113,12 @@ score_topk_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (i >= 2) mbar_wait(s_empty + (i & 1), ((i >> 1) - 1) & 1, p.st);
         tc_fence_after_sync();
         const uint32_t k_addr = smem_u32(k_sm + s * K_BYTES);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * PANEL_BYTES + (kk & 3) * 32;
-          umma_ss(tmem + (uint32_t)((i & 1) * 128), umma_desc_kmajor(k_addr + off), umma_desc_kmajor(q_addr + off), idesc, kk > 0);
+        if (elect_one()) {
+          umma_block_ss<D / 16, PANEL_BYTES>(tmem + (uint32_t)((i & 1) * 128), k_addr, q_addr, idesc);
+          umma_commit(k_empty + s);
+          umma_commit(s_full + (i & 1));
         }
-        umma_commit(k_empty + s);
-        umma_commit(s_full + (i & 1));
+        __syncwarp();
       }
     }
   } else {
