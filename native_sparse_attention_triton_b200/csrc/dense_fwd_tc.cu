@@ -1,18 +1,21 @@
 // Forward of dense varlen GQA attention with the strided-causal mask on the 5th-generation tensor
 // cores (tcgen05.mma, accumulators in tensor memory).
 //
-// CTA = 128 rows = (128/G query tokens) x (G query heads of one KV head), key tiles of 128.
-//   warp 8      : TMA producer (Q once, then K and V tiles through a 3-stage ring)
-//   warp 9      : allocates TMEM; one elected thread issues S = Q K^T (SMEM x SMEM -> TMEM) and
-//                 O += P V (P read from TMEM, V from SMEM MN-major) and commits to mbarriers
-//   warps 0..7  : softmax.  Two threads share a row (TMEM lane), 64 key columns each: they read their logits with
-//                 tcgen05.ld, exchange the row maximum through shared memory, keep a lazily-updated reference maximum (O and l are rescaled only
-//                 when the row maximum grows by more than 2^8), writes P as 16-bit pairs back into
-//                 tensor memory over the logits (tcgen05.st) where the P V instruction reads its A
-//                 operand -- P never touches shared memory -- and finally normalises O.
-// S/P is double-buffered in TMEM so that Q K^T of tile i+1 overlaps the softmax of tile i; the tensor pipe
-// executes one thread's MMAs in issue order, so Q K^T of tile i+2 cannot overtake P V of tile i.
-// TMEM columns: [0,128) S0/P0, [128,256) S1/P1, [256,256+D) O.
+// CTA = two row tiles A and B of 128 rows each; a row tile is (128/G consecutive query tokens) x (G query heads of one
+// KV head); B holds the tokens right after A's.  Key tiles of 128 go through SMEM rings shared by both row tiles.
+//   warp 8      : TMA producer (Q of both tiles once, then K tiles through a ring of 3 and V tiles through a ring of 2)
+//   warp 9      : allocates TMEM; issues, per key tile and row tile, S = Q K^T (SMEM x SMEM -> TMEM) and O += P V
+//                 (P read from TMEM, V from SMEM MN-major), alternating between the two row tiles: while the softmax
+//                 threads of one tile work, the tensor pipe runs the other tile's products
+//   warps 0..3  : softmax of tile A, one thread per row (TMEM lane): a first pass over the 128 logits of the key tile
+//                 finds the row maximum, a second pass reads them again, exponentiates and writes P as 16-bit pairs
+//                 back into tensor memory over the logits, where the P V instruction reads its A operand -- P never
+//                 touches shared memory.  A lazily updated reference maximum is kept: O and l are rescaled only when the
+//                 row maximum grows by more than 2^8.  At the end the threads normalise O and store it
+//   warps 4..7  : the same for tile B
+// The tensor pipe executes one thread's MMAs in issue order, so S(i+1) of a row tile, issued after its P V(i), cannot
+// overwrite P(i) before it has been read.
+// TMEM columns: [0,128) S/P of A, [128,256) S/P of B, [256,256+D) O of A, [384,384+D) O of B.
 #include "attn_tile.cuh"
 #include "dispatch.h"
 #include "host_util.h"
@@ -40,8 +43,8 @@ __device__ __forceinline__ int visible_keys_tc(int t, int Lk, int window, int st
 }
 
 constexpr int kTcKeyTile = 128;
-constexpr int kTcKStages = 3;  // a K tile is free as soon as its Q K^T is done
-constexpr int kTcVStages = 2;  // a V tile is free when its P V is done
+constexpr int kTcKStages = 3;  // a K tile is free as soon as both row tiles' Q K^T are done
+constexpr int kTcVStages = 2;  // a V tile is free when both row tiles' P V are done
 
 template <typename T, int D>
 __global__ void __launch_bounds__(320, 1)
@@ -49,12 +52,11 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     const __grid_constant__ CUtensorMap tmV, DenseFwdTcParams p) {
   constexpr int PANELS = D / 64;
   constexpr int PANEL_BYTES = 128 * 128;            // 128 rows x 128 B
-  constexpr int Q_BYTES = 128 * D * 2;
+  constexpr int Q_BYTES = 128 * D * 2;              // one row tile
   constexpr int KV_BYTES = kTcKeyTile * D * 2;      // one K or V tile
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* q_sm = smem;
-  uint8_t* k_sm = q_sm + Q_BYTES;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* q_sm = smem;                             // [2] row tiles
+  uint8_t* k_sm = q_sm + 2 * Q_BYTES;
   uint8_t* v_sm = k_sm + kTcKStages * KV_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(v_sm + kTcVStages * KV_BYTES);
   uint64_t* q_full = bars;
@@ -62,21 +64,24 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* k_empty = k_full + kTcKStages;
   uint64_t* v_full = k_empty + kTcKStages;
   uint64_t* v_empty = v_full + kTcVStages;
-  uint64_t* s_full = v_empty + kTcVStages;
-  uint64_t* p_full = s_full + 2;
-  uint64_t* pv_done = p_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
-  float* xch = reinterpret_cast<float*>(tmem_slot + 2);  // [2][256] row-maximum / row-sum exchange between the two threads of a row
+  uint64_t* s_full = v_empty + kTcVStages;   // [2] per row tile
+  uint64_t* p_full = s_full + 2;             // [2]
+  uint64_t* pv_done = p_full + 2;            // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (smem_u32(smem) & 1023u) {  // the swizzled operand tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) p.st.raise(kErrSmemLayout);
+    return;
+  }
   const int b = blockIdx.y, h = blockIdx.z;
   const int qs = __ldg(p.cu_q + b), Lq = __ldg(p.cu_q + b + 1) - qs;
   const int ksq = __ldg(p.cu_k + b), Lk = __ldg(p.cu_k + b + 1) - ksq;
-  const int QT = 128 >> p.logG;  // tokens per CTA
+  const int QT = 128 >> p.logG;  // tokens per row tile
   const int qt = gridDim.x - 1 - blockIdx.x;
-  const int q0 = qt * QT;
+  const int q0 = qt * 2 * QT;
   if (q0 >= Lq) return;
-  const int t_hi = min(q0 + QT, Lq) - 1;
+  const int t_hi = min(q0 + 2 * QT, Lq) - 1;
   const int ntiles = (visible_keys_tc(t_hi, Lk, p.window, p.stride, p.causal) + kTcKeyTile - 1) / kTcKeyTile;
 
   if (threadIdx.x == 0) {
@@ -89,9 +94,11 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_init(v_full + s, 1);
       mbar_init(v_empty + s, 1);
     }
-    for (int s = 0; s < 2; ++s) mbar_init(s_full + s, 1);
-    mbar_init(p_full, 8);
-    mbar_init(pv_done, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(s_full + s, 1);
+      mbar_init(p_full + s, 4);
+      mbar_init(pv_done + s, 1);
+    }
     fence_barrier_init();
   }
   if (warp == 9) {
@@ -106,9 +113,12 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == 8) {
     // ===================== TMA producer =====================
     if (lane == 0 && ntiles > 0) {
-      mbar_expect_tx(q_full, Q_BYTES);
+      mbar_expect_tx(q_full, 2 * Q_BYTES);
 #pragma unroll
-      for (int pn = 0; pn < PANELS; ++pn) tma_load_3d(q_sm + pn * PANEL_BYTES, &tmQ, q_full, pn * 64, h * p.G, qs + q0);
+      for (int g = 0; g < 2; ++g)
+#pragma unroll
+        for (int pn = 0; pn < PANELS; ++pn)
+          tma_load_3d(q_sm + g * Q_BYTES + pn * PANEL_BYTES, &tmQ, q_full, pn * 64, h * p.G, qs + q0 + g * QT);
       // K runs one tile ahead of V: tile i's V is requested after tile i+1's K
       for (int i = 0; i <= ntiles; ++i) {
         if (i < ntiles) {
@@ -136,73 +146,79 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const uint32_t idesc_qk = umma_idesc<T>(128, kTcKeyTile, false, false);
       const uint32_t idesc_pv = umma_idesc<T>(128, D, false, true);
       const uint32_t q_addr = smem_u32(q_sm);
-      auto issue_qk = [&](int i) {
+      // S of row tile g for key tile i; the second row tile's product releases the K stage
+      auto issue_qk = [&](int i, int g) {
         const uint32_t k_addr = smem_u32(k_sm + (i % kTcKStages) * KV_BYTES);
-        const uint32_t d_tmem = tmem + (uint32_t)((i & 1) * kTcKeyTile);
         if (elect_one()) {
-          umma_block_ss<D / 16, PANEL_BYTES>(d_tmem, q_addr, k_addr, idesc_qk);
-          umma_commit(k_empty + (i % kTcKStages));
-          umma_commit(s_full + (i & 1));
+          umma_block_ss<D / 16, PANEL_BYTES>(tmem + (uint32_t)(g * 128), q_addr + g * Q_BYTES, k_addr, idesc_qk);
+          if (g == 1) umma_commit(k_empty + (i % kTcKStages));
+          umma_commit(s_full + g);
+        }
+        __syncwarp();
+      };
+      auto issue_pv = [&](int i, int g) {
+        const uint32_t v_addr = smem_u32(v_sm + (i % kTcVStages) * KV_BYTES);
+        const uint32_t p_tmem = tmem + (uint32_t)(g * 128);  // P overwrote the first 64 columns of the tile's S
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < kTcKeyTile / 16; ++kk)
+            umma_ts(tmem + 256 + g * 128, p_tmem + kk * 8, umma_desc_mnmajor(v_addr + kk * 2048, PANEL_BYTES), idesc_pv, i > 0 || kk > 0);
+          if (g == 1) umma_commit(v_empty + (i % kTcVStages));
+          umma_commit(pv_done + g);
         }
         __syncwarp();
       };
       mbar_wait(q_full, 0, p.st);
       mbar_wait(k_full, 0, p.st);
       tc_fence_after_sync();
-      issue_qk(0);
+      issue_qk(0, 0);
+      issue_qk(0, 1);
       for (int i = 0; i < ntiles; ++i) {
-        if (i + 1 < ntiles) {
-          const int n = i + 1;
-          mbar_wait(k_full + (n % kTcKStages), (n / kTcKStages) & 1, p.st);
-          tc_fence_after_sync();
-          issue_qk(n);
-        }
-        mbar_wait(p_full, i & 1, p.st);
-        mbar_wait(v_full + (i % kTcVStages), (i / kTcVStages) & 1, p.st);
-        tc_fence_after_sync();
-        const uint32_t v_addr = smem_u32(v_sm + (i % kTcVStages) * KV_BYTES);
-        const uint32_t p_tmem = tmem + (uint32_t)((i & 1) * kTcKeyTile);  // P overwrote the first 64 columns of this S buffer
-        if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < kTcKeyTile / 16; ++kk)
-            umma_ts(tmem + 256, p_tmem + kk * 8, umma_desc_mnmajor(v_addr + kk * 2048, PANEL_BYTES), idesc_pv, i > 0 || kk > 0);
-          umma_commit(v_empty + (i % kTcVStages));
-          umma_commit(pv_done);
+        for (int g = 0; g < 2; ++g) {
+          mbar_wait(p_full + g, i & 1, p.st);
+          if (g == 0) mbar_wait(v_full + (i % kTcVStages), (i / kTcVStages) & 1, p.st);
+          tc_fence_after_sync();
+          issue_pv(i, g);
+          if (i + 1 < ntiles) {
+            if (g == 0) {
+              mbar_wait(k_full + ((i + 1) % kTcKStages), ((i + 1) / kTcKStages) & 1, p.st);
+              tc_fence_after_sync();
+            }
+            issue_qk(i + 1, g);
+          }
         }
-        __syncwarp();
       }
     }
   } else {
-    // ===================== softmax: two threads per row, 64 key columns each =====================
-    const int half = warp >> 2;
+    // ===================== softmax: one thread per row; warps 0..3 row tile A, warps 4..7 row tile B =====================
+    const int g = warp >> 2;
     const int row = (warp & 3) * 32 + lane;
-    const int tpos = q0 + (row >> p.logG);
+    const int tpos = q0 + g * QT + (row >> p.logG);
     const int head = h * p.G + (row & (p.G - 1));
     const bool valid = tpos < Lq;
     const int nvis = valid ? visible_keys_tc(tpos, Lk, p.window, p.stride, p.causal) : 0;
-    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-    float m_ref = -INFINITY, l = 0.f;  // l: sum over this thread's columns only
+    const uint32_t s_base = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(g * 128);
+    const uint32_t o_base = tmem + ((uint32_t)((warp & 3) * 32) << 16) + 256u + (uint32_t)(g * 128);
+    float m_ref = -INFINITY, l = 0.f;
     for (int i = 0; i < ntiles; ++i) {
-      const int bsel = i & 1;
-      mbar_wait(s_full + bsel, (i >> 1) & 1, p.st);
+      mbar_wait(s_full + g, i & 1, p.st);
       tc_fence_after_sync();
-      uint32_t su[2][32];
-      tmem_ld32(lane_base + bsel * kTcKeyTile + half * 64, su[0]);
-      tmem_ld32(lane_base + bsel * kTcKeyTile + half * 64 + 32, su[1]);
-      tmem_ld_wait();
-      const int lim = nvis - i * kTcKeyTile - half * 64;
+      const int lim = nvis - i * kTcKeyTile;  // columns below lim are visible
+      // ---- pass 1: row maximum of the raw logits (the scale is positive) ----
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int j = 0; j < 64; ++j) {
-        const float v = (j < lim) ? __uint_as_float(su[j >> 5][j & 31]) * p.scale2 : -INFINITY;
-        su[j >> 5][j & 31] = __float_as_uint(v);
-        mx4[j & 3] = fmaxf(mx4[j & 3], v);
+      for (int c = 0; c < 4; ++c) {
+        uint32_t su[32];
+        tmem_ld32(s_base + c * 32, su);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float v = (c * 32 + j < lim) ? __uint_as_float(su[j]) : -INFINITY;
+          mx4[j & 3] = fmaxf(mx4[j & 3], v);
+        }
       }
-      float mt = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // the row maximum needs the other half: exchange through shared memory (buffers alternate per tile)
-      xch[bsel * 256 + half * 128 + row] = mt;
-      asm volatile("bar.sync 1, 256;\n" ::: "memory");
-      mt = fmaxf(mt, xch[bsel * 256 + (half ^ 1) * 128 + row]);
+      const float mt = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale2;
       const bool need = mt > m_ref + 8.f;
       float factor = 1.f;
       if (need) {
@@ -211,54 +227,57 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         l *= factor;
       }
       if (i > 0 && __any_sync(0xffffffffu, need)) {
-        mbar_wait(pv_done, (i - 1) & 1, p.st);  // P V of the previous tile is complete: O is stable
+        mbar_wait(pv_done + g, (i - 1) & 1, p.st);  // P V of the previous key tile is complete: O is stable
         tc_fence_after_sync();
 #pragma unroll
-        for (int c = 0; c < D / 64; ++c) {
+        for (int c = 0; c < D / 32; ++c) {
           uint32_t r[32];
-          tmem_ld32(lane_base + 256 + half * (D / 2) + c * 32, r);
+          tmem_ld32(o_base + c * 32, r);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * factor);
-          tmem_st32(lane_base + 256 + half * (D / 2) + c * 32, r);
+          tmem_st32(o_base + c * 32, r);
         }
         tmem_st_wait();
       }
-      const float msafe = (m_ref == -INFINITY) ? 0.f : m_ref;
-      // P as 16-bit pairs goes back into tensor memory over this thread's share of the tile's logits (keys
-      // 64*half .. 64*half+63 -> packed columns 32*half .. 32*half+31), where the P V product reads its A operand
+      // ---- pass 2: P = exp2(S*scale - m_ref) as 16-bit pairs over the logits: the 32 columns of chunk c become the 16
+      // packed columns [16c, 16c+16), which lie inside chunk c/2 -- already consumed when chunk c is written ----
+      const float nm = (m_ref == -INFINITY) ? 0.f : -m_ref;
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t pk[32];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float p0 = fast_exp2(__uint_as_float(su[(2 * j) >> 5][(2 * j) & 31]) - msafe);
-        const float p1 = fast_exp2(__uint_as_float(su[(2 * j + 1) >> 5][(2 * j + 1) & 31]) - msafe);
-        ls[j & 3] += p0 + p1;
-        pk[j] = DT<T>::pack(p0, p1);
+      for (int c = 0; c < 4; ++c) {
+        uint32_t su[32];
+        tmem_ld32(s_base + c * 32, su);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float p0 = masked_exp2(c * 32 + 2 * j < lim, fmaf(__uint_as_float(su[2 * j]), p.scale2, nm));
+          const float p1 = masked_exp2(c * 32 + 2 * j + 1 < lim, fmaf(__uint_as_float(su[2 * j + 1]), p.scale2, nm));
+          ls[j & 3] += p0 + p1;
+          pk[j] = DT<T>::pack(p0, p1);
+        }
+        tmem_st16(s_base + c * 16, pk);
       }
-      tmem_st32(lane_base + bsel * kTcKeyTile + half * 32, pk);
       tmem_st_wait();
       l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(p_full + g);
     }
-    // ---- epilogue: O / l (the row sum is the sum of the two halves) ----
+    // ---- epilogue: O / l ----
     if (ntiles > 0) {
-      mbar_wait(pv_done, (ntiles - 1) & 1, p.st);
+      mbar_wait(pv_done + g, (ntiles - 1) & 1, p.st);
       tc_fence_after_sync();
     }
-    xch[(ntiles & 1) * 256 + half * 128 + row] = l;
-    asm volatile("bar.sync 1, 256;\n" ::: "memory");
-    l += xch[(ntiles & 1) * 256 + (half ^ 1) * 128 + row];
     const float inv = l > 0.f ? 1.f / l : 0.f;
-    if (valid && half == 0) p.lse[(long long)(qs + tpos) * p.Hq + head] = l > 0.f ? m_ref + log2f(l) : -INFINITY;
-    T* orow = static_cast<T*>(p.o) + (long long)(qs + tpos) * p.o_sn + (long long)head * p.o_sh + half * (D / 2);
+    if (valid) p.lse[(long long)(qs + tpos) * p.Hq + head] = l > 0.f ? m_ref + log2f(l) : -INFINITY;
+    T* orow = static_cast<T*>(p.o) + (long long)(qs + tpos) * p.o_sn + (long long)head * p.o_sh;
 #pragma unroll
-    for (int c = 0; c < D / 64; ++c) {
+    for (int c = 0; c < D / 32; ++c) {
       uint32_t r[32];
       if (ntiles > 0) {
-        tmem_ld32(lane_base + 256 + half * (D / 2) + c * 32, r);
+        tmem_ld32(o_base + c * 32, r);
         tmem_ld_wait();
       } else {
 #pragma unroll
@@ -294,11 +313,11 @@ static int launch_dense_fwd_tc(const void* q, const void* k, const void* v, cons
   if (rc) return rc;
   rc = make_tmap_3d(&tmV, DT<T>::kTmapType, v, D, p.Hkv, Nk, S[5], S[4], 64, 1, kTcKeyTile);
   if (rc) return rc;
-  const size_t smem = 1024 + 128 * D * 2 + (kTcKStages + kTcVStages) * kTcKeyTile * D * 2 + 32 * sizeof(uint64_t) + 512 * sizeof(float);
+  const size_t smem = 2 * 128 * D * 2 + (kTcKStages + kTcVStages) * kTcKeyTile * D * 2 + 32 * sizeof(uint64_t);
   auto kern = dense_fwd_tc_kernel<T, D>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_rc(e);
-  dim3 grid((max_seqlen_q + QT - 1) / QT, p.B, p.Hkv);
+  dim3 grid((max_seqlen_q + 2 * QT - 1) / (2 * QT), p.B, p.Hkv);
   { LaunchScope ls_("dense_fwd_tc", stream); kern<<<grid, 320, smem, stream>>>(tmQ, tmK, tmV, p); }
   return cuda_rc(cudaGetLastError());
 }
