@@ -255,14 +255,27 @@ dense_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tmem_ld32(lane_base + 256 + half * 64 + 32, su[1]);
         tmem_ld_wait();
         const float4* nl4 = reinterpret_cast<const float4*>(nlse_sh + ms * 128 + half * 64);
+        // tiles every key of the warp sees in full (all but those on the mask's edge) skip the mask instructions
+        if (__all_sync(0xffffffffu, clo == 0 && chi == 128)) {
 #pragma unroll
-        for (int j4 = 0; j4 < 16; ++j4) {
-          const float4 nl = nl4[j4];
-          const int j = 4 * j4;
-          pf[j + 0] = masked_exp2((unsigned)(j + 0 - clo_rel) < span, fmaf(__uint_as_float(su[j >> 5][(j + 0) & 31]), p.scale2, nl.x));
-          pf[j + 1] = masked_exp2((unsigned)(j + 1 - clo_rel) < span, fmaf(__uint_as_float(su[j >> 5][(j + 1) & 31]), p.scale2, nl.y));
-          pf[j + 2] = masked_exp2((unsigned)(j + 2 - clo_rel) < span, fmaf(__uint_as_float(su[j >> 5][(j + 2) & 31]), p.scale2, nl.z));
-          pf[j + 3] = masked_exp2((unsigned)(j + 3 - clo_rel) < span, fmaf(__uint_as_float(su[j >> 5][(j + 3) & 31]), p.scale2, nl.w));
+          for (int j4 = 0; j4 < 16; ++j4) {
+            const float4 nl = nl4[j4];
+            const int j = 4 * j4;
+            pf[j + 0] = fast_exp2(fmaf(__uint_as_float(su[j >> 5][(j + 0) & 31]), p.scale2, nl.x));
+            pf[j + 1] = fast_exp2(fmaf(__uint_as_float(su[j >> 5][(j + 1) & 31]), p.scale2, nl.y));
+            pf[j + 2] = fast_exp2(fmaf(__uint_as_float(su[j >> 5][(j + 2) & 31]), p.scale2, nl.z));
+            pf[j + 3] = fast_exp2(fmaf(__uint_as_float(su[j >> 5][(j + 3) & 31]), p.scale2, nl.w));
+          }
+        } else {
+#pragma unroll
+          for (int j4 = 0; j4 < 16; ++j4) {
+            const float4 nl = nl4[j4];
+            const int j = 4 * j4;
+            pf[j + 0] = masked_exp2((unsigned)(j + 0 - clo_rel) < span, fmaf(__uint_as_float(su[j >> 5][(j + 0) & 31]), p.scale2, nl.x));
+            pf[j + 1] = masked_exp2((unsigned)(j + 1 - clo_rel) < span, fmaf(__uint_as_float(su[j >> 5][(j + 1) & 31]), p.scale2, nl.y));
+            pf[j + 2] = masked_exp2((unsigned)(j + 2 - clo_rel) < span, fmaf(__uint_as_float(su[j >> 5][(j + 2) & 31]), p.scale2, nl.z));
+            pf[j + 3] = masked_exp2((unsigned)(j + 3 - clo_rel) < span, fmaf(__uint_as_float(su[j >> 5][(j + 3) & 31]), p.scale2, nl.w));
+          }
         }
         uint32_t pk[32];
 #pragma unroll

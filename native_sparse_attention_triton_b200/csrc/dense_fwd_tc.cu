@@ -16,6 +16,8 @@
 // The tensor pipe executes one thread's MMAs in issue order, so S(i+1) of a row tile, issued after its P V(i), cannot
 // overwrite P(i) before it has been read.
 // TMEM columns: [0,128) S/P of A, [128,256) S/P of B, [256,256+D) O of A, [384,384+D) O of B.
+#include <type_traits>
+
 #include "attn_tile.cuh"
 #include "dispatch.h"
 #include "host_util.h"
@@ -205,19 +207,26 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_wait(s_full + g, i & 1, p.st);
       tc_fence_after_sync();
       const int lim = nvis - i * kTcKeyTile;  // columns below lim are visible
+      // Key tiles that every row of the warp sees in full (all but those on the mask's edge) take a path without the
+      // per-element mask instructions.
+      const bool full = __all_sync(0xffffffffu, lim >= kTcKeyTile);
       // ---- pass 1: row maximum of the raw logits (the scale is positive) ----
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      auto pass1 = [&](auto masked_tag) {
+        constexpr bool MASKED = decltype(masked_tag)::value;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t su[32];
-        tmem_ld32(s_base + c * 32, su);
-        tmem_ld_wait();
+        for (int c = 0; c < 4; ++c) {
+          uint32_t su[32];
+          tmem_ld32(s_base + c * 32, su);
+          tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float v = (c * 32 + j < lim) ? __uint_as_float(su[j]) : -INFINITY;
-          mx4[j & 3] = fmaxf(mx4[j & 3], v);
+          for (int j = 0; j < 32; ++j) {
+            const float v = (!MASKED || c * 32 + j < lim) ? __uint_as_float(su[j]) : -INFINITY;
+            mx4[j & 3] = fmaxf(mx4[j & 3], v);
+          }
         }
-      }
+      };
+      if (full) pass1(std::false_type{}); else pass1(std::true_type{});
       const float mt = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale2;
       const bool need = mt > m_ref + 8.f;
       float factor = 1.f;
@@ -244,21 +253,26 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       // packed columns [16c, 16c+16), which lie inside chunk c/2 -- already consumed when chunk c is written ----
       const float nm = (m_ref == -INFINITY) ? 0.f : -m_ref;
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
+      auto pass2 = [&](auto masked_tag) {
+        constexpr bool MASKED = decltype(masked_tag)::value;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t su[32];
-        tmem_ld32(s_base + c * 32, su);
-        tmem_ld_wait();
-        uint32_t pk[16];
+        for (int c = 0; c < 4; ++c) {
+          uint32_t su[32];
+          tmem_ld32(s_base + c * 32, su);
+          tmem_ld_wait();
+          uint32_t pk[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float p0 = masked_exp2(c * 32 + 2 * j < lim, fmaf(__uint_as_float(su[2 * j]), p.scale2, nm));
-          const float p1 = masked_exp2(c * 32 + 2 * j + 1 < lim, fmaf(__uint_as_float(su[2 * j + 1]), p.scale2, nm));
-          ls[j & 3] += p0 + p1;
-          pk[j] = DT<T>::pack(p0, p1);
+          for (int j = 0; j < 16; ++j) {
+            const float x0 = fmaf(__uint_as_float(su[2 * j]), p.scale2, nm), x1 = fmaf(__uint_as_float(su[2 * j + 1]), p.scale2, nm);
+            const float p0 = MASKED ? masked_exp2(c * 32 + 2 * j < lim, x0) : fast_exp2(x0);
+            const float p1 = MASKED ? masked_exp2(c * 32 + 2 * j + 1 < lim, x1) : fast_exp2(x1);
+            ls[j & 3] += p0 + p1;
+            pk[j] = DT<T>::pack(p0, p1);
+          }
+          tmem_st16(s_base + c * 16, pk);
         }
-        tmem_st16(s_base + c * 16, pk);
-      }
+      };
+      if (full) pass2(std::false_type{}); else pass2(std::true_type{});
       tmem_st_wait();
       l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       tc_fence_before_sync();

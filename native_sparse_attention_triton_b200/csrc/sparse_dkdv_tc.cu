@@ -308,8 +308,14 @@ sparse_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(s_empty + bsel);
+        // tiles every row of the warp sees in full (all but the block on the diagonal) skip the mask instructions
+        if (__all_sync(0xffffffffu, lim >= 32)) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) pf[j] = masked_exp2(j < lim, fmaf(__uint_as_float(su[j]), p.scale2, nlse));
+          for (int j = 0; j < 32; ++j) pf[j] = fast_exp2(fmaf(__uint_as_float(su[j]), p.scale2, nlse));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) pf[j] = masked_exp2(j < lim, fmaf(__uint_as_float(su[j]), p.scale2, nlse));
+        }
         uint32_t pw[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) pw[j] = DT<T>::pack(pf[2 * j], pf[2 * j + 1]);
