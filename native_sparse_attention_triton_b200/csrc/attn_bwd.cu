@@ -225,7 +225,7 @@ struct SparseBwdParams {
   Status st;
 };
 
-template <typename T, int D, int WARPS>
+template <typename T, int D, int WARPS, int KBUFS>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 sparse_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, SparseBwdParams p) {
   constexpr int TILE_BYTES = kKeyTile * D * 2;
@@ -233,16 +233,18 @@ sparse_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  uint8_t* kbuf = smem + warp * 2 * TILE_BYTES;
-  uint8_t* vbuf = kbuf + TILE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + WARPS * 2 * TILE_BYTES);
-  uint64_t* bar = bars + warp;
-  int* tiles = reinterpret_cast<int*>(bars + WARPS) + warp * kMaxTilesBwd;
+  uint8_t* kbuf = smem + warp * (KBUFS + 1) * TILE_BYTES;  // KBUFS K tiles, then one V tile
+  uint8_t* vbuf = kbuf + KBUFS * TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + WARPS * (KBUFS + 1) * TILE_BYTES);
+  uint64_t* barK = bars + (KBUFS + 1) * warp;  // [KBUFS]
+  uint64_t* barV = barK + KBUFS;
+  int* tiles = reinterpret_cast<int*>(bars + (KBUFS + 1) * WARPS) + warp * kMaxTilesBwd;
   const int n = blockIdx.x * WARPS + warp;
   if (n >= p.N) return;
   const int h = blockIdx.y;
   if (lane == 0) {
-    mbar_init(bar, 1);
+    for (int kb = 0; kb < KBUFS; ++kb) mbar_init(barK + kb, 1);
+    mbar_init(barV, 1);
     fence_barrier_init();
   }
   __syncwarp();
@@ -275,15 +277,25 @@ sparse_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     ntiles = kMaxTilesBwd;
   }
   __syncwarp();
-  auto issue = [&](int kpos) {
-    mbar_expect_tx(bar, 2 * TILE_BYTES);
+  // K and V tiles have a barrier each: dP = dO V^T comes first, so the next V tile is requested as soon as dP is done
+  // and travels under the S, dS and dQ products.  With one K buffer the next K tile is requested at the end of a tile
+  // and travels under the next dP; with two it is requested a whole tile ahead.
+  auto issue_k = [&](int i) {
+    uint8_t* dst = kbuf + (i % KBUFS) * TILE_BYTES;
+    mbar_expect_tx(barK + (i % KBUFS), TILE_BYTES);
 #pragma unroll
-    for (int pn = 0; pn < PANELS; ++pn) {
-      tma_load_3d(kbuf + pn * (kKeyTile * 128), &tmK, bar, pn * 64, h, s0 + kpos);
-      tma_load_3d(vbuf + pn * (kKeyTile * 128), &tmV, bar, pn * 64, h, s0 + kpos);
-    }
+    for (int pn = 0; pn < PANELS; ++pn) tma_load_3d(dst + pn * (kKeyTile * 128), &tmK, barK + (i % KBUFS), pn * 64, h, s0 + tiles[i]);
   };
-  if (ntiles > 0 && lane == 0) issue(tiles[0]);
+  auto issue_v = [&](int kpos) {
+    mbar_expect_tx(barV, TILE_BYTES);
+#pragma unroll
+    for (int pn = 0; pn < PANELS; ++pn) tma_load_3d(vbuf + pn * (kKeyTile * 128), &tmV, barV, pn * 64, h, s0 + kpos);
+  };
+  if (ntiles > 0 && lane == 0) {
+    issue_v(tiles[0]);
+    issue_k(0);
+    if (KBUFS > 1 && ntiles > 1) issue_k(1);
+  }
 
   const int r_lo = lane >> 2;
   const bool rok[2] = {r_lo < p.G, r_lo + 8 < p.G};
@@ -313,12 +325,39 @@ sparse_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
   uint32_t phase = 0;
   for (int i = 0; i < ntiles; ++i) {
     const int kpos = tiles[i];
-    mbar_wait(bar, phase, p.st);
     const int limv = min(kKeyTile, t - kpos + 1);
-    const int lim[2] = {limv, limv};
-    dq_tile<T, D>(qf, dof, dq, smem_u32(kbuf), smem_u32(vbuf), lim, lse2, delta, p.scale2, p.sm_scale);
+    const int c0 = (lane & 3) * 2;
+    float dp[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dp[j][0] = dp[j][1] = dp[j][2] = dp[j][3] = 0.f;
+    mbar_wait(barV, phase, p.st);
+    mma_nk<T, 8, D / 16, kKeyTile>(dp, dof, smem_u32(vbuf), 0, 0);
     __syncwarp();
-    if (i + 1 < ntiles && lane == 0) issue(tiles[i + 1]);
+    if (i + 1 < ntiles && lane == 0) issue_v(tiles[i + 1]);
+    const uint32_t kb_addr = smem_u32(kbuf + (i % KBUFS) * TILE_BYTES);
+    mbar_wait(barK + (i % KBUFS), (i / KBUFS) & 1, p.st);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      float sacc[4][4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
+      mma_nk<T, 4, D / 16, kKeyTile>(sacc, qf, kb_addr, 32 * half, 0);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = e >> 1;
+          const int col = 32 * half + j * 8 + c0 + (e & 1);
+          const float pr = masked_exp2(col < limv, sacc[j][e] * p.scale2 - lse2[r]);
+          sacc[j][e] = pr * (dp[half * 4 + j][e] - delta[r]) * p.sm_scale;
+        }
+      }
+      uint32_t dsf[2][4];
+      acc_to_a_frags<T, 2>(dsf, sacc);
+      mma_kn<T, D / 8, 2, kKeyTile>(dq, dsf, kb_addr, 32 * half, 0);
+    }
+    __syncwarp();
+    if (i + KBUFS < ntiles && lane == 0) issue_k(i + KBUFS);
     phase ^= 1;
   }
   T* dbase = static_cast<T*>(p.dq) + (long long)n * p.dq_sn + (long long)h * p.G * p.dq_sh;
@@ -768,6 +807,10 @@ static int run_dense_bwd(const void* q, const void* k, const void* v, const void
   return cuda_rc(cudaGetLastError());
 }
 
+#ifndef NSA_DQ_KBUFS
+#define NSA_DQ_KBUFS 1
+#define NSA_DQ_WARPS ((D == 128) ? 7 : 8)
+#endif
 constexpr int kSparseChunk = 512;  // tokens of one block's list handled by one CTA
 
 // Token windows of the inverted index: as many tokens as keep the Q and dO rows of one KV-head group (G heads) within
@@ -837,15 +880,16 @@ static int run_sparse_bwd(const void* q, const void* k, const void* v, const voi
   { LaunchScope ls_("index_fill", stream); index_scatter_kernel<true><<<(unsigned)((hn + 255) / 256), 256, 0, stream>>>(ip); }
   if ((e = cudaGetLastError()) != cudaSuccess) return cuda_rc(e);
   {
-    constexpr int WARPS = (D == 128) ? 6 : 8;
+    constexpr int KBUFS = NSA_DQ_KBUFS;
+    constexpr int WARPS = NSA_DQ_WARPS;
     constexpr int TILE_BYTES = kKeyTile * D * 2;
     CUtensorMap tmK, tmV;
     int rc = make_tmap_3d(&tmK, DT<T>::kTmapType, k, D, Hkv, N, S[3], S[2], 64, 1, kKeyTile);
     if (rc) return rc;
     rc = make_tmap_3d(&tmV, DT<T>::kTmapType, v, D, Hkv, N, S[5], S[4], 64, 1, kKeyTile);
     if (rc) return rc;
-    const size_t smem = 1024 + WARPS * 2 * TILE_BYTES + WARPS * sizeof(uint64_t) + WARPS * kMaxTilesBwd * sizeof(int);
-    auto kern = sparse_dq_kernel<T, D, WARPS>;
+    const size_t smem = 1024 + WARPS * (KBUFS + 1) * TILE_BYTES + (KBUFS + 1) * WARPS * sizeof(uint64_t) + WARPS * kMaxTilesBwd * sizeof(int);
+    auto kern = sparse_dq_kernel<T, D, WARPS, KBUFS>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return cuda_rc(e);
     dim3 grid((N + WARPS - 1) / WARPS, Hkv);

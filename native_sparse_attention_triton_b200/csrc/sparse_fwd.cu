@@ -134,7 +134,7 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
 template <typename T, int D>
 static int launch_sparse_fwd(const void* k, const void* v, long long k_sn, long long k_sh, long long v_sn, long long v_sh,
                              SparseFwdParams p, cudaStream_t stream) {
-  constexpr int WARPS = (D == 128) ? 6 : 8;
+  constexpr int WARPS = (D == 128) ? 7 : 8;  // as many private K+V tile pairs as shared memory holds
   constexpr int TILE_BYTES = kKeyTile * D * 2;
   CUtensorMap tmK, tmV;
   int rc = make_tmap_3d(&tmK, DT<T>::kTmapType, k, D, p.Hkv, p.N, k_sh, k_sn, 64, 1, kKeyTile);
