@@ -30,7 +30,7 @@ constexpr int kDqVStages = 2;
 template <typename T, int D>
 __global__ void __launch_bounds__(320, 1)
 dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
-                   const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, DenseBwdParams p) {
+                   const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, DenseBwdParams p) {
   constexpr int KT = 128;
   constexpr int PANELS = D / 64;
   constexpr int PANEL_BYTES = 128 * 128;
@@ -52,7 +52,9 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* dp_full = s_empty + 1;
   uint64_t* ds_full = dp_full + 1;
   uint64_t* all_done = ds_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(all_done + 1);
+  uint64_t* o_full = all_done + 1;   // the O rows, staged in the last K stage for the delta computation
+  uint64_t* o_done = o_full + 1;     // ... and read by all softmax warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (smem_u32(smem) & 1023u) {  // the swizzled operand tiles need a 1024-byte aligned base
@@ -88,6 +90,8 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(dp_full, 1);
     mbar_init(ds_full, 8);
     mbar_init(all_done, 1);
+    mbar_init(o_full, 1);
+    mbar_init(o_done, 8);
     fence_barrier_init();
   }
   if (warp == 9) {
@@ -108,9 +112,16 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tma_load_3d(q_sm + pn * PANEL_BYTES, &tmQ, qdo_full, pn * 64, h * p.G, qs + q0);
         tma_load_3d(do_sm + pn * PANEL_BYTES, &tmDO, qdo_full, pn * 64, h * p.G, qs + q0);
       }
+      // delta = rowsum(O * dO) is computed from SMEM: the O rows borrow the last K stage, which the ring needs only
+      // for its third tile
+      uint8_t* o_sm = k_sm + (kDqKStages - 1) * ROW_BYTES;
+      mbar_expect_tx(o_full, ROW_BYTES);
+#pragma unroll
+      for (int pn = 0; pn < PANELS; ++pn) tma_load_3d(o_sm + pn * PANEL_BYTES, &tmO, o_full, pn * 64, h * p.G, qs + q0);
       for (int i = 0; i < ntiles; ++i) {
         const int sk = i % kDqKStages, sv = i % kDqVStages;
         if (i >= kDqKStages) mbar_wait(k_empty + sk, ((i / kDqKStages) - 1) & 1, p.st);
+        if (i == kDqKStages - 1) mbar_wait(o_done, 0, p.st);
         mbar_expect_tx(k_full + sk, ROW_BYTES);
 #pragma unroll
         for (int pn = 0; pn < PANELS; ++pn)
@@ -195,26 +206,33 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const bool valid = tpos < Lq;
     const int nvis = valid ? visible(tpos) : 0;
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-    // ---- delta = sum_d O * dO of this row (each of the two threads sums half of the row) ----
+    // ---- delta = sum_d O * dO of this row, from the SMEM copies (each of the two threads sums half of the row) ----
+    const float lse2 = valid ? __ldg(p.lse + (long long)(qs + tpos) * p.Hq + head) : INFINITY;
     float part = 0.f;
-    if (valid) {
-      const T* orow = static_cast<const T*>(p.o) + (long long)(qs + tpos) * p.o_sn + (long long)head * p.o_sh + half * (D / 2);
-      const T* drow = static_cast<const T*>(p.dout) + (long long)(qs + tpos) * p.do_sn + (long long)head * p.do_sh + half * (D / 2);
+    if (ntiles > 0) {
+      mbar_wait(qdo_full, 0, p.st);
+      mbar_wait(o_full, 0, p.st);
+      const uint32_t o_addr = smem_u32(k_sm + (kDqKStages - 1) * ROW_BYTES), d_addr = smem_u32(do_sm);
 #pragma unroll
       for (int c = 0; c < D / 16; ++c) {
-        const uint4 ov = __ldg(reinterpret_cast<const uint4*>(orow) + c), dv = __ldg(reinterpret_cast<const uint4*>(drow) + c);
-        const uint32_t ou[4] = {ov.x, ov.y, ov.z, ov.w}, du[4] = {dv.x, dv.y, dv.z, dv.w};
+        const int ci = half * (D / 16) + c;  // 16-byte chunk of the row
+        const uint32_t off = (ci >> 3) * PANEL_BYTES + row * 128 + (((ci & 7) ^ (row & 7)) << 4);
+        uint32_t ou[4], du[4];
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];\n" : "=r"(ou[0]), "=r"(ou[1]), "=r"(ou[2]), "=r"(ou[3]) : "r"(o_addr + off));
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];\n" : "=r"(du[0]), "=r"(du[1]), "=r"(du[2]), "=r"(du[3]) : "r"(d_addr + off));
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float2 a = DT<T>::unpack(ou[e]), bb = DT<T>::unpack(du[e]);
           part += a.x * bb.x + a.y * bb.y;
         }
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(o_done);
     }
+    if (!valid) part = 0.f;
     delta_sh[half * 128 + row] = part;
     asm volatile("bar.sync 1, 256;\n" ::: "memory");
     const float delta = delta_sh[row] + delta_sh[128 + row];
-    const float lse2 = valid ? __ldg(p.lse + (long long)(qs + tpos) * p.Hq + head) : INFINITY;
     if (valid && half == 0) p.ld[(long long)(qs + tpos) * p.Hq + head] = make_float2(lse2, delta);
     const float nlse = -lse2;
     const float ndsc = -delta * p.sm_scale;
@@ -295,11 +313,13 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 template <typename T, int D>
 static int launch_dense_dq_tc(const void* k, const void* v, long long k_sn, long long k_sh, long long v_sn, long long v_sh,
                               int total_q, int total_k, int max_seqlen_q, DenseBwdParams p, cudaStream_t stream) {
-  CUtensorMap tmQ, tmDO, tmK, tmV;
+  CUtensorMap tmQ, tmDO, tmO, tmK, tmV;
   const int QT = 128 / p.G;
   int rc = make_tmap_3d(&tmQ, DT<T>::kTmapType, p.q, D, p.Hq, total_q, p.q_sh, p.q_sn, 64, p.G, QT);
   if (rc) return rc;
   rc = make_tmap_3d(&tmDO, DT<T>::kTmapType, p.dout, D, p.Hq, total_q, p.do_sh, p.do_sn, 64, p.G, QT);
+  if (rc) return rc;
+  rc = make_tmap_3d(&tmO, DT<T>::kTmapType, p.o, D, p.Hq, total_q, p.o_sh, p.o_sn, 64, p.G, QT);
   if (rc) return rc;
   rc = make_tmap_3d(&tmK, DT<T>::kTmapType, k, D, p.Hkv, total_k, k_sh, k_sn, 64, 1, 128);
   if (rc) return rc;
@@ -310,7 +330,7 @@ static int launch_dense_dq_tc(const void* k, const void* v, long long k_sn, long
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_rc(e);
   dim3 grid((max_seqlen_q + QT - 1) / QT, p.B, p.Hkv);
-  { LaunchScope ls_("dense_dq_tc", stream); kern<<<grid, 320, smem, stream>>>(tmQ, tmDO, tmK, tmV, p); }
+  { LaunchScope ls_("dense_dq_tc", stream); kern<<<grid, 320, smem, stream>>>(tmQ, tmDO, tmO, tmK, tmV, p); }
   return cuda_rc(cudaGetLastError());
 }
 
