@@ -187,6 +187,16 @@ def config_record():
 
 
 # kernel -> (bound, algorithmic work per launch as a function of the FLOP model); see DESIGN.md
+# DRAM bytes (read + write) per launch measured by ncu on the 16384-token case (profiles/attention_kernels_16k_tokens_set_full.md).
+# These kernels' DRAM traffic is their linear-in-tokens streams (Q, O, dO, dQ rows; K/V re-reads hit L2), so the figure is
+# scaled by tokens / 16384 for the workload at hand.
+NCU_DRAM_BYTES_16K = {
+    "dense_fwd_tc": 0.271e9 + 230.1e6, "score_topk_tc": 0.275e9 + 10.4e6, "sparse_fwd": 0.306e9 + 241.0e6,
+    "sparse_dq": 0.851e9 + 259.3e6, "sparse_dkdv_tc": 1.623e9 + 116.8e6, "dense_dq_tc": 0.815e9 + 253.8e6,
+    "dense_dkdv_tc": 0.553e9 + 7.3e6,
+}
+
+
 def kernel_work(name, f):
     cmp_f, sel_f, lin_f = f["cmp_fwd"], f["sel_fwd"], f["lin_fwd"]
     table = {
@@ -416,8 +426,11 @@ def main():
         avg_ms = per_kernel[dom]["ms_per_step"] / n_launch
         if work:
             achieved = work[1] / 1e12 / (avg_ms / 1e3)
+            traffic = NCU_DRAM_BYTES_16K.get(dom)
             roofline = dict(kernel=dom, bound=work[0], achieved=achieved, peak=pk["tc_sustained"], unit="TFLOP/s",
-                            frac=achieved / pk["tc_sustained"], traffic=None, launch_ms=avg_ms, peak_source=pk["source"],
+                            frac=achieved / pk["tc_sustained"], traffic=None if traffic is None else traffic * N / 16384,
+                            traffic_unit="bytes of DRAM read+write per launch (ncu capture at 16384 tokens, scaled by tokens)",
+                            launch_ms=avg_ms, peak_source=pk["source"],
                             note="peak = sustained cuBLAS bf16 figure (kernel timed inside a long step)")
         else:
             roofline = dict(kernel=dom, bound="hbm", achieved=None, peak=pk["hbm"], unit="GB/s", frac=None, traffic=None,
