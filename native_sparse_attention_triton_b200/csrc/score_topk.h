@@ -28,4 +28,8 @@ struct ScoreParams {
 int score_topk_tc(const void* q, const void* k, long long k_sn, long long k_sh, int Nq, int Nk, int max_seqlen_q, int head_dim,
                   int dtype, ScoreParams p, cudaStream_t stream);
 
+// tcgen05 implementation with two row tiles per CTA (score_topk_pp_tc.cu); same contract, tighter shared-memory limit.
+int score_topk_pp_tc(const void* q, const void* k, long long k_sn, long long k_sh, int Nq, int Nk, int max_seqlen_q, int head_dim,
+                     int dtype, ScoreParams p, cudaStream_t stream);
+
 }  // namespace nsa
