@@ -20,18 +20,37 @@ namespace nsa {
 // ------------------------------------------------------------------------------------------------
 // bias[h, n] = sum_r a[h, r] * Wm[h, r, n]     (linear: a = pe flattened, Wm = W, R = ks*d, NO = d)
 // ------------------------------------------------------------------------------------------------
+// One CTA of 256 threads per (head, 8 output columns): a thread walks the rows r = tid, tid + 256, ... with one 16-byte
+// load of W per row; the 256 partial sums of each column are reduced in a fixed order (deterministic).
 template <typename T>
-__global__ void linear_bias_kernel(const T* __restrict__ pe, const T* __restrict__ w, T* __restrict__ bias, int R, int NO) {
-  extern __shared__ float red[];  // [blockDim.y][NO]
-  const int h = blockIdx.x, n = threadIdx.x;
-  float acc = 0.f;
-  for (int r = threadIdx.y; r < R; r += blockDim.y)
-    acc += DT<T>::to_float(pe[(size_t)h * R + r]) * DT<T>::to_float(w[((size_t)h * R + r) * NO + n]);
-  red[threadIdx.y * NO + n] = acc;
+__global__ void __launch_bounds__(256) linear_bias_kernel(const T* __restrict__ pe, const T* __restrict__ w, T* __restrict__ bias, int R, int NO) {
+  __shared__ float red[8][8];
+  const int h = blockIdx.x, n0 = blockIdx.y * 8;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int r = threadIdx.x; r < R; r += 256) {
+    const float a = DT<T>::to_float(pe[(size_t)h * R + r]);
+    const uint4 wv = __ldg(reinterpret_cast<const uint4*>(w + ((size_t)h * R + r) * NO + n0));
+    const uint32_t wu[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = DT<T>::unpack(wu[e]);
+      acc[2 * e] += a * f.x;
+      acc[2 * e + 1] += a * f.y;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
+  if ((threadIdx.x & 31) == 0)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) red[threadIdx.x >> 5][j] = acc[j];
   __syncthreads();
-  if (threadIdx.y == 0) {
-    for (int y = 1; y < blockDim.y; ++y) acc += red[y * NO + n];
-    bias[(size_t)h * NO + n] = DT<T>::from_float(acc);
+  if (threadIdx.x < 8) {
+    float sum = 0.f;
+#pragma unroll
+    for (int wp = 0; wp < 8; ++wp) sum += red[wp][threadIdx.x];
+    bias[(size_t)h * NO + n0 + threadIdx.x] = DT<T>::from_float(sum);
   }
 }
 
@@ -199,8 +218,7 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(PoolFwdParams p) {
 template <typename T, int D>
 static int launch_linear_fwd(LinFwdParams p, const void* pe, void* bias_scratch, int B, int max_ylen, cudaStream_t stream) {
   if (pe) {
-    dim3 blk(D, 1024 / D);
-    { LaunchScope ls_("linear_bias", stream); linear_bias_kernel<T><<<p.H, blk, blk.y * D * sizeof(float), stream>>>(
+    { LaunchScope ls_("linear_bias", stream); linear_bias_kernel<T><<<dim3(p.H, D / 8), 256, 0, stream>>>(
         static_cast<const T*>(pe), static_cast<const T*>(p.w), static_cast<T*>(bias_scratch), p.ks * D, D); }
     p.bias = bias_scratch;
   } else {

@@ -18,18 +18,36 @@
 
 namespace nsa {
 
-// dbias[h, n] = sum_m dy[m, h, n]   (fp32), one CTA per head
+// dbias[h, n] = sum_m dy[m, h, n]   (fp32).  One CTA of 256 threads per (head, 8 columns): a thread walks the rows
+// m = tid, tid + 256, ... with one 16-byte load per row; fixed-order reduction (deterministic).
 template <typename T>
-__global__ void colsum_kernel(const T* __restrict__ dy, float* __restrict__ dbias, int M, int H, int D) {
-  extern __shared__ float red[];
-  const int h = blockIdx.x, n = threadIdx.x;
-  float acc = 0.f;
-  for (int m = threadIdx.y; m < M; m += blockDim.y) acc += DT<T>::to_float(dy[((size_t)m * H + h) * D + n]);
-  red[threadIdx.y * D + n] = acc;
+__global__ void __launch_bounds__(256) colsum_kernel(const T* __restrict__ dy, float* __restrict__ dbias, int M, int H, int D) {
+  __shared__ float red[8][8];
+  const int h = blockIdx.x, n0 = blockIdx.y * 8;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int m = threadIdx.x; m < M; m += 256) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(dy + ((size_t)m * H + h) * D + n0));
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = DT<T>::unpack(u[e]);
+      acc[2 * e] += f.x;
+      acc[2 * e + 1] += f.y;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
+  if ((threadIdx.x & 31) == 0)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) red[threadIdx.x >> 5][j] = acc[j];
   __syncthreads();
-  if (threadIdx.y == 0) {
-    for (int y = 1; y < blockDim.y; ++y) acc += red[y * D + n];
-    dbias[h * D + n] = acc;
+  if (threadIdx.x < 8) {
+    float sum = 0.f;
+#pragma unroll
+    for (int wp = 0; wp < 8; ++wp) sum += red[wp][threadIdx.x];
+    dbias[h * D + n0 + threadIdx.x] = sum;
   }
 }
 
@@ -301,8 +319,7 @@ __global__ void __launch_bounds__(256) pool_dw_kernel(PoolBwdParams p) {
 template <typename T, int D>
 static int run_linear_bwd(LinBwdParams p, void* dpe, float* dbias, int total_y, int max_len, cudaStream_t stream) {
   if (p.pe) {
-    dim3 blk(D, 1024 / D);
-    { LaunchScope ls_("colsum", stream); colsum_kernel<T><<<p.H, blk, blk.y * D * sizeof(float), stream>>>(static_cast<const T*>(p.dy), dbias, total_y, p.H, D); }
+    { LaunchScope ls_("colsum", stream); colsum_kernel<T><<<dim3(p.H, D / 8), 256, 0, stream>>>(static_cast<const T*>(p.dy), dbias, total_y, p.H, D); }
     p.dbias = dbias;
     const long long hr = (long long)p.H * p.ks * D;
     { LaunchScope ls_("linear_dpe", stream); linear_dpe_kernel<T><<<(unsigned)((hr + 255) / 256), 256, 0, stream>>>(dbias, static_cast<const T*>(p.w),
@@ -329,8 +346,7 @@ static int run_linear_bwd(LinBwdParams p, void* dpe, float* dbias, int total_y, 
 template <typename T, int D>
 static int run_pool_bwd(PoolBwdParams p, float* dbias, int total_y, cudaStream_t stream) {
   if (p.pe) {
-    dim3 blk(D, 1024 / D);
-    { LaunchScope ls_("colsum", stream); colsum_kernel<T><<<p.H, blk, blk.y * D * sizeof(float), stream>>>(static_cast<const T*>(p.dy), dbias, total_y, p.H, D); }
+    { LaunchScope ls_("colsum", stream); colsum_kernel<T><<<dim3(p.H, D / 8), 256, 0, stream>>>(static_cast<const T*>(p.dy), dbias, total_y, p.H, D); }
     p.dbias = dbias;
   }
   const long long total = (long long)p.N * p.H * (D / 8);
