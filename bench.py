@@ -164,7 +164,8 @@ def cpu_baseline_record(sample_tokens, seconds):
 def run_reference(args, rank, world):
     if rank != 0:
         return
-    sample = 1024
+    sample = CPU_SAMPLE_TOKENS
+    cpu_chain_seconds(256)   # untimed: thread pool start-up, first-call costs
     for _ in range(min(args.warmup, 1)):
         cpu_chain_seconds(sample)
     times = [cpu_chain_seconds(sample) for _ in range(max(1, args.steps))]
