@@ -216,6 +216,37 @@ def kernel_work(name, f):
     return table.get(name)
 
 
+def window_microbench(ops, dev, tokens):
+    """Sliding-window branch (the third branch of an NSA layer) at the layer's shape: one sequence, 64q/4kv heads, d=128,
+    window 512, forward + backward.  Useful FLOPs count unmasked (query, key) pairs only: 2 GEMMs forward, 5 backward."""
+    g = torch.Generator().manual_seed(7)
+    Hq, Hkv, d, W = WORKLOAD["Hq"], WORKLOAD["Hkv"], WORKLOAD["d"], 512
+    q, k, v, do = (torch.randn(tokens, h, d, generator=g).to(torch.bfloat16).to(dev) for h in (Hq, Hkv, Hkv, Hq))
+    for x in (q, k, v):
+        x.requires_grad_(True)
+    cu = torch.tensor([0, tokens], dtype=torch.int32, device=dev)
+
+    def step():
+        q.grad = k.grad = v.grad = None
+        ops.sliding_window_attention(q, k, v, cu, tokens, W).backward(do)
+
+    for _ in range(3):
+        step()
+    pkg_lib = sys.modules["native_sparse_attention_triton_b200"]._lib
+    pkg_lib.profile(True)
+    reps = 5
+    for _ in range(reps):
+        step()
+    torch.cuda.synchronize()
+    kern = pkg_lib.profile_collect()
+    pkg_lib.profile(False)
+    pairs = sum(min(t + 1, W + 1) for t in range(tokens))
+    flops = 3.5 * 4 * d * Hq * pairs
+    ms = sum(v_[1] for v_ in kern.values()) / reps
+    return dict(tokens=tokens, window=W, kernel_ms=ms, useful_tflops=flops / 1e12 / (ms / 1e3),
+                per_kernel_ms={k_: v_[1] / reps for k_, v_ in kern.items()})
+
+
 def decode_microbench(ops, dev):
     """The three single-token operators on (a) the bandwidth-sized case of the reference's decode self-tests
     (batch 76, cache 8192, 32q/4kv heads, d=128, block 64, top-16, ragged lengths) and (b) the shapes of the
@@ -404,11 +435,12 @@ def main():
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     e2e_ms = float(e2e_t.item())
     status = pkg.device_status()
-    decode = None
+    decode = window = None
     if rank == 0 and not args.no_decode:
         del t, t2, sets, host
         torch.cuda.empty_cache()
         decode = decode_microbench(ops, dev)
+        window = window_microbench(ops, dev, N)
 
     if rank != 0:
         if dist is not None:
@@ -448,7 +480,7 @@ def main():
                          note="host->device copy of step s+1 overlaps the compute of step s (two input sets)"),
                 gpu_launches=launches, roofline=roofline, cpu_baseline=cpu,
                 tokens_per_s=world * N / (ms / 1e3), useful_tflops_per_gpu=useful_tflops,
-                frac_of_tc_peak=useful_tflops / pk["tc_sustained"], per_kernel_ms=per_kernel, decode=decode,
+                frac_of_tc_peak=useful_tflops / pk["tc_sustained"], per_kernel_ms=per_kernel, decode=decode, sliding_window=window,
                 hbm_peak_gb_per_s=pk["hbm"], device_status=status)
     print(json.dumps(line), flush=True)
     if dist is not None:

@@ -169,6 +169,20 @@ int nsa_varlen_attn_bwd(const void* q, const void* k, const void* v, const void*
                         int causal, int window, int stride, const long long* strides, float sm_scale, int dtype,
                         void* stream);
 
+/* Sliding-window branch of the NSA layer: causal varlen self-attention where query t sees keys t - window_left .. t
+ * (window_left + 1 keys).  The reference has no operator of its own here: its layer calls the third-party
+ * flash_attn.flash_attn_varlen_func(causal=True, window_size=(window_size, -1)),
+ * native_sparse_attention/module/native_sparse_attention.py:213-223; these two entry points replace that call.
+ * Same tensors, strides, lse convention and workspace (nsa_varlen_attn_bwd_workspace with total_k = total_q) as
+ * nsa_varlen_attn_fwd / nsa_varlen_attn_bwd with one cu_seqlens for queries and keys.  head_dim 128 only (-2 otherwise). */
+int nsa_window_attn_fwd(const void* q, const void* k, const void* v, const int* cu_seqlens, void* o, float* lse,
+                        int total_len, int batch, int max_seqlen, int num_q_heads, int num_kv_heads, int head_dim,
+                        int window_left, const long long* strides, float sm_scale, int dtype, void* stream);
+int nsa_window_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                        const int* cu_seqlens, void* dq, void* dk, void* dv, void* workspace, long long workspace_bytes,
+                        int total_len, int batch, int max_seqlen, int num_q_heads, int num_kv_heads, int head_dim,
+                        int window_left, const long long* strides, float sm_scale, int dtype, void* stream);
+
 /* Bytes of scratch nsa_topk_sparse_attn_bwd needs (fp32 dk/dv accumulators, (lse, delta) pairs, inverted index). */
 long long nsa_topk_sparse_attn_bwd_workspace(int total_len, int batch, int num_q_heads, int num_kv_heads,
                                              int head_dim, int topk, int block_size);

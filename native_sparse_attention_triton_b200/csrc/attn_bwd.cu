@@ -735,7 +735,7 @@ static size_t dense_ws_bytes(int total_q, int total_k, int Hq, int Hkv, int D) {
 template <typename T, int D>
 static int run_dense_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
                          const int* cu_q, const int* cu_k, void* dq, void* dk, void* dv, void* ws, int total_q, int total_k,
-                         int batch, int max_q, int max_k, int Hq, int Hkv, int causal, int window, int stride,
+                         int batch, int max_q, int max_k, int Hq, int Hkv, int causal, int window, int stride, int left,
                          const long long* S, float sm_scale, cudaStream_t stream) {
   // S: q_n q_h k_n k_h v_n v_h o_n o_h do_n do_h dq_n dq_h dk_n dk_h dv_n dv_h
   const int G = Hq / Hkv;
@@ -754,9 +754,10 @@ static int run_dense_bwd(const void* q, const void* k, const void* v, const void
   p.B = batch; p.Hq = Hq; p.Hkv = Hkv; p.G = G;
   p.logG = 0;
   while ((1 << p.logG) < G) ++p.logG;
-  p.window = window; p.stride = stride; p.causal = causal;
+  p.window = window; p.stride = stride; p.causal = causal; p.left = left;
   p.scale2 = sm_scale * kLog2e; p.sm_scale = sm_scale;
   p.st.word = status_word();
+  if (left >= 0 && (legacy_mma() || D != 128)) return kUnsupported;  // the sliding window lives in the tcgen05 kernels only
   if (!legacy_mma()) {
     const int dt = DT<T>::kTmapType == CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 ? NSA_DTYPE_BF16 : NSA_DTYPE_FP16;
     const int rc = dense_dq_tc(k, v, S[2], S[3], S[4], S[5], total_q, total_k, max_q, D, dt, p, stream);
@@ -787,7 +788,7 @@ static int run_dense_bwd(const void* q, const void* k, const void* v, const void
   int chunk = 256;
   while (chunk < 1024 && chunk * 16 < max_q) chunk <<= 1;
   d.chunk = chunk;
-  d.window = window; d.stride = stride; d.causal = causal;
+  d.window = window; d.stride = stride; d.causal = causal; d.left = left;
   d.scale2 = p.scale2; d.sm_scale = sm_scale; d.st = p.st;
   const long long ds[8] = {S[0], S[1], S[2], S[3], S[4], S[5], S[8], S[9]};
   dim3 grid((max_k + kKeyTile - 1) / kKeyTile, (max_q + chunk - 1) / chunk, batch * Hkv);
@@ -900,7 +901,7 @@ static int run_sparse_bwd(const void* q, const void* k, const void* v, const voi
   d.ld = ld; d.dk32 = dk32; d.dv32 = dv32; d.cu_q = cu; d.cu_k = cu;
   d.cu_blocks = cu_blocks; d.offsets = offsets; d.item_base = item_base; d.list = list;
   d.B = batch; d.Hq = Hq; d.Hkv = Hkv; d.G = G; d.TB = TB; d.NW = NW; d.chunk = kSparseChunk; d.block_size = block_size;
-  d.window = 1; d.stride = 1; d.causal = 1;
+  d.window = 1; d.stride = 1; d.causal = 1; d.left = -1;
   d.scale2 = p.scale2; d.sm_scale = sm_scale; d.st = p.st;
   const long long ds[8] = {S[0], S[1], S[2], S[3], S[4], S[5], S[8], S[9]};
   // upper bound on work items: every selection in a full chunk, plus one partial chunk per (head, block)
@@ -926,12 +927,12 @@ extern "C" long long nsa_varlen_attn_bwd_workspace(int total_q, int total_k, int
   return (long long)nsa::dense_ws_bytes(total_q, total_k, num_q_heads, num_kv_heads, head_dim);
 }
 
-extern "C" int nsa_varlen_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
-                                   const float* lse, const int* cu_seqlens_q, const int* cu_seqlens_k, void* dq, void* dk,
-                                   void* dv, void* workspace, long long workspace_bytes, int total_q, int total_k, int batch,
-                                   int max_seqlen_q, int max_seqlen_k, int num_q_heads, int num_kv_heads, int head_dim,
-                                   int causal, int window, int stride, const long long* strides, float sm_scale, int dtype,
-                                   void* stream) {
+static int varlen_attn_bwd_common(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                                  const float* lse, const int* cu_seqlens_q, const int* cu_seqlens_k, void* dq, void* dk,
+                                  void* dv, void* workspace, long long workspace_bytes, int total_q, int total_k, int batch,
+                                  int max_seqlen_q, int max_seqlen_k, int num_q_heads, int num_kv_heads, int head_dim,
+                                  int causal, int window, int stride, int left, const long long* strides, float sm_scale,
+                                  int dtype, void* stream) {
   using namespace nsa;
   if (!q || !k || !v || !o || !dout || !lse || !cu_seqlens_q || !cu_seqlens_k || !dq || !dk || !dv || !workspace || !strides)
     return kInvalid;
@@ -939,12 +940,35 @@ extern "C" int nsa_varlen_attn_bwd(const void* q, const void* k, const void* v, 
   if (num_kv_heads <= 0 || num_q_heads % num_kv_heads) return kInvalid;
   const int G = num_q_heads / num_kv_heads;
   if (G > 16 || (G & (G - 1))) return kUnsupported;
+  if (left >= 0 && (!causal || window != 1 || stride != 1)) return kUnsupported;
   for (int i = 0; i < 16; ++i)
     if (strides[i] % 8) return kInvalid;
   if (workspace_bytes < (long long)dense_ws_bytes(total_q, total_k, num_q_heads, num_kv_heads, head_dim)) return kWorkspace;
   return NSA_DISPATCH_T_D(dtype, head_dim, run_dense_bwd, q, k, v, o, dout, lse, cu_seqlens_q, cu_seqlens_k, dq, dk, dv,
                           workspace, total_q, total_k, batch, max_seqlen_q, max_seqlen_k, num_q_heads, num_kv_heads, causal,
-                          window, stride, strides, sm_scale, static_cast<cudaStream_t>(stream));
+                          window, stride, left, strides, sm_scale, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nsa_varlen_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                                   const float* lse, const int* cu_seqlens_q, const int* cu_seqlens_k, void* dq, void* dk,
+                                   void* dv, void* workspace, long long workspace_bytes, int total_q, int total_k, int batch,
+                                   int max_seqlen_q, int max_seqlen_k, int num_q_heads, int num_kv_heads, int head_dim,
+                                   int causal, int window, int stride, const long long* strides, float sm_scale, int dtype,
+                                   void* stream) {
+  return varlen_attn_bwd_common(q, k, v, o, dout, lse, cu_seqlens_q, cu_seqlens_k, dq, dk, dv, workspace, workspace_bytes,
+                                total_q, total_k, batch, max_seqlen_q, max_seqlen_k, num_q_heads, num_kv_heads, head_dim,
+                                causal, window, stride, -1, strides, sm_scale, dtype, stream);
+}
+
+extern "C" int nsa_window_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                                   const float* lse, const int* cu_seqlens, void* dq, void* dk, void* dv, void* workspace,
+                                   long long workspace_bytes, int total_len, int batch, int max_seqlen, int num_q_heads,
+                                   int num_kv_heads, int head_dim, int window_left, const long long* strides, float sm_scale,
+                                   int dtype, void* stream) {
+  if (window_left < 0) return nsa::kInvalid;
+  return varlen_attn_bwd_common(q, k, v, o, dout, lse, cu_seqlens, cu_seqlens, dq, dk, dv, workspace, workspace_bytes, total_len,
+                                total_len, batch, max_seqlen, max_seqlen, num_q_heads, num_kv_heads, head_dim, 1, 1, 1,
+                                window_left, strides, sm_scale, dtype, stream);
 }
 
 extern "C" long long nsa_topk_sparse_attn_bwd_workspace(int total_len, int batch, int num_q_heads, int num_kv_heads,

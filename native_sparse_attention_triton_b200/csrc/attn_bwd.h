@@ -22,6 +22,7 @@ struct DkdvParams {
   int NW;  // sparse: token windows per KV head; bin x = (head * NW + window) * TB + block
 
   int window, stride, causal;
+  int left;  // dense pass only; >= 0: sliding window (key >= t - left, plain causal mask), < 0: none
   float scale2, sm_scale;
   Status st;
 };
@@ -40,6 +41,7 @@ struct DenseBwdParams {
   long long q_sn, q_sh, o_sn, o_sh, do_sn, do_sh, dq_sn, dq_sh;
   int B, Hq, Hkv, G, logG;
   int window, stride, causal;
+  int left;  // >= 0: sliding window (key >= t - left, plain causal mask), < 0: none
   float scale2, sm_scale;
   Status st;
 };

@@ -81,7 +81,8 @@ dense_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const int t_first = p.causal ? kpos * p.stride + p.window - 1 : 0;
   const int c_lo = blockIdx.y * p.chunk;
   const int tok_begin = max(c_lo, t_first);
-  const int tok_end = min(c_lo + p.chunk, Lq);
+  // sliding window: key j is seen by tokens up to j + left only
+  const int tok_end = p.left >= 0 ? min(min(c_lo + p.chunk, Lq), kpos + kvalid + p.left) : min(c_lo + p.chunk, Lq);
   if (tok_end <= tok_begin) return;
   const int ntiles = (tok_end - tok_begin + TPT - 1) / TPT;
 
@@ -241,7 +242,8 @@ dense_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const int tok0 = tok_begin + i * TPT;
       // visible columns of this thread: [clo, chi) in tile columns, shifted to the thread's own 64
       const int clo = max(0, thr - tok0) << logG;
-      const int chi = key_ok ? (min(TPT, tok_end - tok0) << logG) : 0;
+      int chi = key_ok ? (min(TPT, tok_end - tok0) << logG) : 0;
+      if (p.left >= 0) chi = min(chi, max(0, kpos + key + p.left - tok0 + 1) << logG);
       const int clo_rel = clo - half * 64;
       const unsigned span = chi > clo ? (unsigned)(chi - clo) : 0u;
 

@@ -73,7 +73,9 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     return t < p.window - 1 ? 0 : min(Lk, (t - p.window + 1) / p.stride + 1);
   };
   const int t_hi = min(q0 + QT, Lq) - 1;
-  const int ntiles = (visible(t_hi) + KT - 1) / KT;
+  // with a sliding window the first key tiles are invisible to every row of the CTA: start at tile kt0
+  const int kt0 = p.left >= 0 ? max(0, q0 - p.left) / KT : 0;
+  const int ntiles = max(0, (visible(t_hi) + KT - 1) / KT - kt0);
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
@@ -125,12 +127,12 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mbar_expect_tx(k_full + sk, ROW_BYTES);
 #pragma unroll
         for (int pn = 0; pn < PANELS; ++pn)
-          tma_load_3d(k_sm + sk * ROW_BYTES + pn * PANEL_BYTES, &tmK, k_full + sk, pn * 64, h, ksq + i * KT);
+          tma_load_3d(k_sm + sk * ROW_BYTES + pn * PANEL_BYTES, &tmK, k_full + sk, pn * 64, h, ksq + (kt0 + i) * KT);
         if (i >= kDqVStages) mbar_wait(v_empty + sv, ((i / kDqVStages) - 1) & 1, p.st);
         mbar_expect_tx(v_full + sv, ROW_BYTES);
 #pragma unroll
         for (int pn = 0; pn < PANELS; ++pn)
-          tma_load_3d(v_sm + sv * ROW_BYTES + pn * PANEL_BYTES, &tmV, v_full + sv, pn * 64, h, ksq + i * KT);
+          tma_load_3d(v_sm + sv * ROW_BYTES + pn * PANEL_BYTES, &tmV, v_full + sv, pn * 64, h, ksq + (kt0 + i) * KT);
       }
     }
   } else if (warp == 9) {
@@ -250,9 +252,11 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(s_empty);
-        const int lim = nvis - i * KT - half * 64;
+        const int lim = nvis - (kt0 + i) * KT - half * 64;  // columns below lim are visible ...
+        const int lo = p.left >= 0 ? tpos - p.left - (kt0 + i) * KT - half * 64 : 0;  // ... from column lo on
 #pragma unroll
-        for (int j = 0; j < 64; ++j) pf[j] = masked_exp2(j < lim, fmaf(__uint_as_float(su[j >> 5][j & 31]), p.scale2, nlse));
+        for (int j = 0; j < 64; ++j)
+          pf[j] = masked_exp2(j < lim && j >= lo, fmaf(__uint_as_float(su[j >> 5][j & 31]), p.scale2, nlse));
       }
       // ---- dS phase ----
       mbar_wait(dp_full, i & 1, p.st);

@@ -180,7 +180,7 @@ static int launch_dense_fwd(const void* k, const void* v, long long k_sn, long l
 // tcgen05 implementation (dense_fwd_tc.cu)
 int varlen_attn_fwd_tc(const void* q, const void* k, const void* v, const int* cu_q, const int* cu_k, void* o, float* lse,
                        int total_q, int total_k, int batch, int max_seqlen_q, int Hq, int Hkv, int head_dim, int causal,
-                       int window, int stride, const long long* strides, float sm_scale, int dtype, cudaStream_t stream);
+                       int window, int stride, int left, const long long* strides, float sm_scale, int dtype, cudaStream_t stream);
 
 // The mma.sync kernel of this file stays selectable (environment variable NSA_B200_LEGACY_MMA=1) for A/B measurements.
 static bool use_legacy_mma() {
@@ -190,12 +190,14 @@ static bool use_legacy_mma() {
 
 }  // namespace nsa
 
-extern "C" int nsa_varlen_attn_fwd(const void* q, const void* k, const void* v, const int* cu_seqlens_q,
-                                   const int* cu_seqlens_k, void* o, float* lse, int total_q, int total_k, int batch,
-                                   int max_seqlen_q, int num_q_heads, int num_kv_heads, int head_dim, int causal,
-                                   int window, int stride, const long long* strides, float sm_scale, int dtype,
-                                   void* stream) {
+// left >= 0 adds the lower bound key >= t - left (sliding window); only with the plain causal mask and on the tcgen05 kernel
+static int varlen_attn_fwd_common(const void* q, const void* k, const void* v, const int* cu_seqlens_q,
+                                  const int* cu_seqlens_k, void* o, float* lse, int total_q, int total_k, int batch,
+                                  int max_seqlen_q, int num_q_heads, int num_kv_heads, int head_dim, int causal,
+                                  int window, int stride, int left, const long long* strides, float sm_scale, int dtype,
+                                  void* stream) {
   using namespace nsa;
+  if (left >= 0 && (!causal || window != 1 || stride != 1 || use_legacy_mma())) return kUnsupported;
   if (!q || !cu_seqlens_q || !cu_seqlens_k || !o || !lse || !strides) return kInvalid;
   if (total_q <= 0 || batch <= 0 || max_seqlen_q <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads) return kInvalid;
   if (window < 1 || stride < 1) return kInvalid;
@@ -217,8 +219,25 @@ extern "C" int nsa_varlen_attn_fwd(const void* q, const void* k, const void* v, 
   if ((p.q_sn | p.q_sh | p.o_sn | p.o_sh) % 8 || !aligned16(q) || !aligned16(o)) return kInvalid;
   if (!use_legacy_mma())
     return varlen_attn_fwd_tc(q, k, v, cu_seqlens_q, cu_seqlens_k, o, lse, total_q, total_k, batch, max_seqlen_q, num_q_heads,
-                              num_kv_heads, head_dim, causal, window, stride, strides, sm_scale, dtype,
+                              num_kv_heads, head_dim, causal, window, stride, left, strides, sm_scale, dtype,
                               static_cast<cudaStream_t>(stream));
   return NSA_DISPATCH_T_D(dtype, head_dim, launch_dense_fwd, k, v, strides[2], strides[3], strides[4], strides[5],
                           total_k, max_seqlen_q, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nsa_varlen_attn_fwd(const void* q, const void* k, const void* v, const int* cu_seqlens_q,
+                                   const int* cu_seqlens_k, void* o, float* lse, int total_q, int total_k, int batch,
+                                   int max_seqlen_q, int num_q_heads, int num_kv_heads, int head_dim, int causal,
+                                   int window, int stride, const long long* strides, float sm_scale, int dtype,
+                                   void* stream) {
+  return varlen_attn_fwd_common(q, k, v, cu_seqlens_q, cu_seqlens_k, o, lse, total_q, total_k, batch, max_seqlen_q, num_q_heads,
+                                num_kv_heads, head_dim, causal, window, stride, -1, strides, sm_scale, dtype, stream);
+}
+
+extern "C" int nsa_window_attn_fwd(const void* q, const void* k, const void* v, const int* cu_seqlens, void* o, float* lse,
+                                   int total_len, int batch, int max_seqlen, int num_q_heads, int num_kv_heads, int head_dim,
+                                   int window_left, const long long* strides, float sm_scale, int dtype, void* stream) {
+  if (window_left < 0) return nsa::kInvalid;
+  return varlen_attn_fwd_common(q, k, v, cu_seqlens, cu_seqlens, o, lse, total_len, total_len, batch, max_seqlen, num_q_heads,
+                                num_kv_heads, head_dim, 1, 1, 1, window_left, strides, sm_scale, dtype, stream);
 }

@@ -34,6 +34,7 @@ struct DenseFwdTcParams {
   long long o_sn, o_sh;
   int B, Hq, Hkv, G, logG;
   int window, stride, causal;
+  int left;  // >= 0: sliding window, a query also needs key >= t - left (plain causal mask only); < 0: no lower bound
   float scale2;
   Status st;
 };
@@ -84,7 +85,9 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int q0 = qt * 2 * QT;
   if (q0 >= Lq) return;
   const int t_hi = min(q0 + 2 * QT, Lq) - 1;
-  const int ntiles = (visible_keys_tc(t_hi, Lk, p.window, p.stride, p.causal) + kTcKeyTile - 1) / kTcKeyTile;
+  // with a sliding window the first key tiles are invisible to every row of the CTA: start at tile kt0
+  const int kt0 = p.left >= 0 ? max(0, q0 - p.left) / kTcKeyTile : 0;
+  const int ntiles = max(0, (visible_keys_tc(t_hi, Lk, p.window, p.stride, p.causal) + kTcKeyTile - 1) / kTcKeyTile - kt0);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -129,7 +132,7 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           mbar_expect_tx(k_full + s, KV_BYTES);
 #pragma unroll
           for (int pn = 0; pn < PANELS; ++pn)
-            tma_load_3d(k_sm + s * KV_BYTES + pn * PANEL_BYTES, &tmK, k_full + s, pn * 64, h, ksq + i * kTcKeyTile);
+            tma_load_3d(k_sm + s * KV_BYTES + pn * PANEL_BYTES, &tmK, k_full + s, pn * 64, h, ksq + (kt0 + i) * kTcKeyTile);
         }
         if (i >= 1) {
           const int j = i - 1, s = j % kTcVStages;
@@ -137,7 +140,7 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           mbar_expect_tx(v_full + s, KV_BYTES);
 #pragma unroll
           for (int pn = 0; pn < PANELS; ++pn)
-            tma_load_3d(v_sm + s * KV_BYTES + pn * PANEL_BYTES, &tmV, v_full + s, pn * 64, h, ksq + j * kTcKeyTile);
+            tma_load_3d(v_sm + s * KV_BYTES + pn * PANEL_BYTES, &tmV, v_full + s, pn * 64, h, ksq + (kt0 + j) * kTcKeyTile);
         }
       }
     }
@@ -206,10 +209,11 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     for (int i = 0; i < ntiles; ++i) {
       mbar_wait(s_full + g, i & 1, p.st);
       tc_fence_after_sync();
-      const int lim = nvis - i * kTcKeyTile;  // columns below lim are visible
+      const int lim = nvis - (kt0 + i) * kTcKeyTile;  // columns below lim are visible ...
+      const int lo = p.left >= 0 ? tpos - p.left - (kt0 + i) * kTcKeyTile : 0;  // ... from column lo on
       // Key tiles that every row of the warp sees in full (all but those on the mask's edge) take a path without the
       // per-element mask instructions.
-      const bool full = __all_sync(0xffffffffu, lim >= kTcKeyTile);
+      const bool full = __all_sync(0xffffffffu, lim >= kTcKeyTile && lo <= 0);
       // ---- pass 1: row maximum of the raw logits (the scale is positive) ----
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       auto pass1 = [&](auto masked_tag) {
@@ -221,7 +225,7 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const float v = (!MASKED || c * 32 + j < lim) ? __uint_as_float(su[j]) : -INFINITY;
+            const float v = (!MASKED || (c * 32 + j < lim && c * 32 + j >= lo)) ? __uint_as_float(su[j]) : -INFINITY;
             mx4[j & 3] = fmaxf(mx4[j & 3], v);
           }
         }
@@ -264,8 +268,8 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const float x0 = fmaf(__uint_as_float(su[2 * j]), p.scale2, nm), x1 = fmaf(__uint_as_float(su[2 * j + 1]), p.scale2, nm);
-            const float p0 = MASKED ? masked_exp2(c * 32 + 2 * j < lim, x0) : fast_exp2(x0);
-            const float p1 = MASKED ? masked_exp2(c * 32 + 2 * j + 1 < lim, x1) : fast_exp2(x1);
+            const float p0 = MASKED ? masked_exp2(c * 32 + 2 * j < lim && c * 32 + 2 * j >= lo, x0) : fast_exp2(x0);
+            const float p1 = MASKED ? masked_exp2(c * 32 + 2 * j + 1 < lim && c * 32 + 2 * j + 1 >= lo, x1) : fast_exp2(x1);
             ls[j & 3] += p0 + p1;
             pk[j] = DT<T>::pack(p0, p1);
           }
@@ -339,14 +343,14 @@ static int launch_dense_fwd_tc(const void* q, const void* k, const void* v, cons
 // entry used by nsa_varlen_attn_fwd (dense_fwd.cu)
 int varlen_attn_fwd_tc(const void* q, const void* k, const void* v, const int* cu_q, const int* cu_k, void* o, float* lse,
                        int total_q, int total_k, int batch, int max_seqlen_q, int Hq, int Hkv, int head_dim, int causal,
-                       int window, int stride, const long long* strides, float sm_scale, int dtype, cudaStream_t stream) {
+                       int window, int stride, int left, const long long* strides, float sm_scale, int dtype, cudaStream_t stream) {
   DenseFwdTcParams p;
   p.o = o; p.lse = lse; p.cu_q = cu_q; p.cu_k = cu_k;
   p.o_sn = strides[6]; p.o_sh = strides[7];
   p.B = batch; p.Hq = Hq; p.Hkv = Hkv; p.G = Hq / Hkv;
   p.logG = 0;
   while ((1 << p.logG) < p.G) ++p.logG;
-  p.window = window; p.stride = stride; p.causal = causal;
+  p.window = window; p.stride = stride; p.causal = causal; p.left = left;
   p.scale2 = sm_scale * kLog2e;
   p.st.word = status_word();
   return NSA_DISPATCH_T_D(dtype, head_dim, launch_dense_fwd_tc, q, k, v, strides, total_q, total_k, max_seqlen_q, p, stream);

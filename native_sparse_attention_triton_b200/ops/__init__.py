@@ -3,6 +3,7 @@ from .compress import avgpool_compress, linear_compress, weightedpool_compress
 from .compressed_attention import compressed_attention
 from .decode import compressed_attention_decode, flash_attention_decode, topk_sparse_attention_decode
 from .flash_attention import flash_attention_varlen
+from .sliding_window import sliding_window_attention
 from .topk_sparse_attention import topk_sparse_attention
 from .utils import get_compressed_seqlens
 
@@ -11,6 +12,7 @@ __all__ = [
     "weightedpool_compress",
     "linear_compress",
     "flash_attention_varlen",
+    "sliding_window_attention",
     "compressed_attention",
     "topk_sparse_attention",
     "flash_attention_decode",

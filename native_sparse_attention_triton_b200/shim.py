@@ -71,5 +71,45 @@ def _patch_loaded_modules(fns):
                     table[key] = fns[fn_name]
 
 
+def window_attention_adapter(fallback):
+    """A function with flash_attn.flash_attn_varlen_func's calling convention that runs the sliding-window branch of the
+    NSA layer (causal self-attention, ``window_size=(W, -1)``, head_dim 128, no other option) on this package's kernels
+    and passes every other call on to ``fallback`` (the function it replaces)."""
+    def flash_attn_varlen_func(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, *args, causal=False,
+                               window_size=(-1, -1), **kwargs):
+        ours = (not args and not kwargs and causal and window_size[0] >= 0 and window_size[1] in (-1, 0)
+                and cu_seqlens_q is cu_seqlens_k and q.shape[-1] == 128 and q.shape[0] == k.shape[0])
+        if ours:
+            return _ops.sliding_window_attention(q, k, v, cu_seqlens_q.to(_int32()), max_seqlen_q, window_size[0])
+        if fallback is None:
+            raise NotImplementedError("only the sliding-window call of the NSA layer is implemented")
+        return fallback(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, *args, causal=causal,
+                        window_size=window_size, **kwargs)
+    return flash_attn_varlen_func
+
+
+def _int32():
+    import torch
+    return torch.int32
+
+
+def install_sliding_window():
+    """Opt-in: also route the NSA layer's sliding-window branch, which the reference sends to the third-party flash_attn
+    package (native_sparse_attention/module/native_sparse_attention.py:15,213-223), to this package.  Only the layer
+    module is touched, and only its call with ``causal=True, window_size=(W, -1)`` is taken over.  Call after the
+    reference's module package has been imported.  Returns the number of modules patched."""
+    patched = 0
+    for name, mod in list(sys.modules.items()):
+        if mod is None or not name.startswith(_PKG + ".module"):
+            continue
+        fn = getattr(mod, "flash_attn_varlen_func", None)
+        if fn is not None and hasattr(mod, "topk_sparse_attention") and not getattr(fn, "__nsa_b200_shim__", False):
+            adapter = window_attention_adapter(fn)
+            adapter.__nsa_b200_shim__ = True
+            mod.flash_attn_varlen_func = adapter
+            patched += 1
+    return patched
+
+
 def installed() -> bool:
     return getattr(sys.modules.get(f"{_PKG}.ops"), "__nsa_b200_shim__", False)

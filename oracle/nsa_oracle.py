@@ -286,6 +286,32 @@ def flash_attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q=Non
     return torch.cat(outs, 0).to(q.dtype)
 
 
+def sliding_window_attention(q, k, v, cu_seqlens, window_size, sm_scale=None):
+    """Causal varlen self-attention with a sliding window: query ``i`` sees keys ``i - window_size .. i``.
+
+    The reference delegates this branch to the third-party flash_attn package
+    (native_sparse_attention/module/native_sparse_attention.py:213-223, ``causal=True``,
+    ``window_size=(window_size, -1)``); this restates flash_attn's published mask semantics for equal query and key
+    lengths (key j visible iff i - left <= j <= i).  Parity unpinned by the reference's own tests (it stores no
+    vectors for this branch); the GPU tests compare against this function only.
+    """
+    N, Hq, d = q.shape
+    G = Hq // k.shape[1]
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(d)
+    outs = []
+    for b in range(cu_seqlens.numel() - 1):
+        s, e = int(cu_seqlens[b]), int(cu_seqlens[b + 1])
+        logits = torch.einsum("qhd,khd->hqk", q[s:e].float(), k[s:e].float().repeat_interleave(G, 1)) * sm_scale
+        i = torch.arange(e - s)[:, None]
+        j = torch.arange(e - s)[None, :]
+        m = (j <= i) & (j >= i - window_size)
+        logits = logits.masked_fill(~m[None], float("-inf"))
+        p = logits.softmax(-1).nan_to_num(0)
+        outs.append(torch.einsum("hqk,khd->qhd", p, v[s:e].float().repeat_interleave(G, 1)))
+    return torch.cat(outs, 0).to(q.dtype)
+
+
 # --------------------------------------------------------------------------- #
 # single-token (decode) operators (rows a5 - a7)
 # --------------------------------------------------------------------------- #

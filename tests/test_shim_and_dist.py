@@ -22,6 +22,8 @@ def test_shim_routes_reference_imports(tmp_path, monkeypatch):
         from native_sparse_attention.ops import flash_attention_decode, avgpool_compress, weightedpool_compress
         from native_sparse_attention.ops.triton.utils import get_compressed_seqlens
         COMPRESS_TYPE_TO_FUNC = {"avgpool": avgpool_compress, "weightedpool": weightedpool_compress, "linear": linear_compress}
+        def flash_attn_varlen_func(*args, **kwargs):   # stands in for the third-party function the layer imports
+            return ("third party", args, kwargs)
     """))
     monkeypatch.syspath_prepend(str(tmp_path))
     for name in [n for n in sys.modules if n.startswith("native_sparse_attention")]:
@@ -43,6 +45,15 @@ def test_shim_routes_reference_imports(tmp_path, monkeypatch):
     shim.install(patch_loaded=True)
     assert ref_module.linear_compress is ops.linear_compress
     assert ref_module.COMPRESS_TYPE_TO_FUNC["linear"] is ops.linear_compress
+    # opt-in routing of the sliding-window branch: only the layer's own kind of call is taken over
+    assert shim.install_sliding_window() == 1 and shim.install_sliding_window() == 0
+    x = torch.zeros(4, 2, 64)   # head_dim 64: not ours -> passed on to the function that was there before
+    cu = torch.tensor([0, 4], dtype=torch.int32)
+    out = ref_module.flash_attn_varlen_func(x, x, x, cu, cu, 4, 4, causal=True, window_size=(2, -1))
+    assert out[0] == "third party" and out[2] == {"causal": True, "window_size": (2, -1)}
+    with pytest.raises(RuntimeError, match="no CPU path"):   # head_dim 128, causal, windowed: ours (and ours needs CUDA tensors)
+        y = torch.zeros(4, 2, 128, dtype=torch.bfloat16)
+        ref_module.flash_attn_varlen_func(y, y, y, cu, cu, 4, 4, causal=True, window_size=(2, -1))
     for name in [n for n in sys.modules if n.startswith("native_sparse_attention.") or n == "native_sparse_attention"]:
         monkeypatch.delitem(sys.modules, name)
 
