@@ -187,7 +187,7 @@ def config_record():
                 l2_policy="inputs (q alone is 1.07 GB) exceed the 126 MB L2; no explicit flush")
 
 
-# kernel -> (bound, algorithmic work per launch as a function of the FLOP model); see DESIGN.md
+# kernel -> (bound, algorithmic work per launch as a function of the useful-FLOP model of oracle.nsa_oracle.useful_flops)
 # DRAM bytes (read + write) per launch measured by ncu on the 16384-token case (profiles/attention_kernels_16k_tokens_set_full.md).
 # These kernels' DRAM traffic is their linear-in-tokens streams (Q, O, dO, dQ rows; K/V re-reads hit L2), so the figure is
 # scaled by tokens / 16384 for the workload at hand.

@@ -21,15 +21,6 @@ __device__ __forceinline__ uint64_t umma_desc_mnmajor(uint32_t saddr, uint32_t p
          ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 
-// Moves the start address of a descriptor by `bytes` (a multiple of 16).  The start-address field is the low 14 bits in
-// units of 16 bytes; shared memory is smaller than 256 KB, so the sum never carries out of the field and one 32-bit add
-// on the low word is enough.  The issuing thread builds each descriptor once and advances it per MMA: it has a budget of
-// only a few dozen issue slots per MMA before it, not the tensor pipe, becomes the limit.
-__device__ __forceinline__ uint64_t umma_desc_advance(uint64_t desc, uint32_t bytes) {
-  const uint32_t lo = static_cast<uint32_t>(desc) + (bytes >> 4);
-  return (desc & 0xFFFFFFFF00000000ull) | lo;
-}
-
 // ---- instruction descriptor: fp32 accumulate, 16-bit inputs ----
 template <typename T>
 __device__ __forceinline__ constexpr uint32_t umma_idesc(int M, int N, bool a_mn_major, bool b_mn_major) {

@@ -16,13 +16,14 @@ Nothing in the test-suite or the benchmark needs the reference at run time:
 they only read the ``.npz`` files written here.
 """
 import math
+import os
 import sys
 from unittest import mock
 
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("NSA_REFERENCE_CHECKOUT", "reference")
 sys.path.insert(0, REF)
 OUT = __file__.rsplit("/", 1)[0]
 
