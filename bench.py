@@ -468,6 +468,21 @@ def main():
         else:
             roofline = dict(kernel=dom, bound="hbm", achieved=None, peak=pk["hbm"], unit="GB/s", frac=None, traffic=None,
                             launch_ms=avg_ms, peak_source=pk["source"])
+    # every attention kernel against the tensor roofline: useful flops (what the model credits) and executed flops (the
+    # backward passes recompute the logits: dQ executes 3 GEMM units for 2 credited, dK/dV 4 for 3; the score pass 1 for 0)
+    executed_over_useful = {"dense_dq": 1.5, "dense_dkdv": 4.0 / 3.0, "sparse_dq": 1.5, "sparse_dkdv": 4.0 / 3.0}
+    kernel_rooflines = {}
+    for kname, rec in per_kernel.items():
+        work = kernel_work(kname, f)
+        if not work or rec["ms_per_step"] <= 0:
+            continue
+        base = kname[:-3] if kname.endswith("_tc") else kname
+        useful = 0.0 if base == "score_topk" else work[1]
+        executed = work[1] * executed_over_useful.get(base, 1.0)
+        sec_k = rec["ms_per_step"] / 1e3
+        kernel_rooflines[kname] = dict(ms=rec["ms_per_step"], useful_tflops=useful / 1e12 / sec_k,
+                                       executed_tflops=executed / 1e12 / sec_k,
+                                       executed_frac_of_peak=executed / 1e12 / sec_k / pk["tc_sustained"])
     cpu = None
     if not args.no_cpu_baseline:
         sec = cpu_chain_seconds(CPU_SAMPLE_TOKENS if N >= CPU_SAMPLE_TOKENS else N)
@@ -480,7 +495,7 @@ def main():
                          note="host->device copy of step s+1 overlaps the compute of step s (two input sets)"),
                 gpu_launches=launches, roofline=roofline, cpu_baseline=cpu,
                 tokens_per_s=world * N / (ms / 1e3), useful_tflops_per_gpu=useful_tflops,
-                frac_of_tc_peak=useful_tflops / pk["tc_sustained"], per_kernel_ms=per_kernel, decode=decode, sliding_window=window,
+                frac_of_tc_peak=useful_tflops / pk["tc_sustained"], per_kernel_ms=per_kernel, kernel_rooflines=kernel_rooflines, decode=decode, sliding_window=window,
                 hbm_peak_gb_per_s=pk["hbm"], device_status=status)
     print(json.dumps(line), flush=True)
     if dist is not None:

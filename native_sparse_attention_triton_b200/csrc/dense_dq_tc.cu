@@ -254,9 +254,15 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (lane == 0) mbar_arrive(s_empty);
         const int lim = nvis - (kt0 + i) * KT - half * 64;  // columns below lim are visible ...
         const int lo = p.left >= 0 ? tpos - p.left - (kt0 + i) * KT - half * 64 : 0;  // ... from column lo on
+        // tiles every row of the warp sees in full (all but those on the mask's edges) skip the mask instructions
+        if (__all_sync(0xffffffffu, lim >= 64 && lo <= 0)) {
 #pragma unroll
-        for (int j = 0; j < 64; ++j)
-          pf[j] = masked_exp2(j < lim && j >= lo, fmaf(__uint_as_float(su[j >> 5][j & 31]), p.scale2, nlse));
+          for (int j = 0; j < 64; ++j) pf[j] = fast_exp2(fmaf(__uint_as_float(su[j >> 5][j & 31]), p.scale2, nlse));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 64; ++j)
+            pf[j] = masked_exp2(j < lim && j >= lo, fmaf(__uint_as_float(su[j >> 5][j & 31]), p.scale2, nlse));
+        }
       }
       // ---- dS phase ----
       mbar_wait(dp_full, i & 1, p.st);
