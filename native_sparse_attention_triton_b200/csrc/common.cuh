@@ -98,6 +98,22 @@ __device__ __forceinline__ float masked_exp2(bool keep, float x) {
   return keep ? e : 0.f;
 }
 
+// Packed fp32 pairs (sm_100: one instruction for two lanes of FMA / MUL).  The softmax threads of the tcgen05 kernels are
+// bound by issue slots they share with the MMA-issuing warp, so halving their elementwise instruction count matters.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n .reg .b64 ra, rb, rc, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n mov.b64 rc, {%6, %7};\n"
+      " fma.rn.f32x2 rd, ra, rb, rc;\n mov.b64 {%0, %1}, rd;\n}\n"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n .reg .b64 ra, rb, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n mul.rn.f32x2 rd, ra, rb;\n mov.b64 {%0, %1}, rd;\n}\n"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+
 __device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
 
 // largest b such that cu[b] <= n (cu has nseq+1 ascending entries, cu[0] = 0)

@@ -257,7 +257,12 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         // tiles every row of the warp sees in full (all but those on the mask's edges) skip the mask instructions
         if (__all_sync(0xffffffffu, lim >= 64 && lo <= 0)) {
 #pragma unroll
-          for (int j = 0; j < 64; ++j) pf[j] = fast_exp2(fmaf(__uint_as_float(su[j >> 5][j & 31]), p.scale2, nlse));
+          for (int j = 0; j < 64; j += 2) {
+            const float2 x = ffma2(make_float2(__uint_as_float(su[j >> 5][j & 31]), __uint_as_float(su[j >> 5][(j & 31) + 1])),
+                                   make_float2(p.scale2, p.scale2), make_float2(nlse, nlse));
+            pf[j] = fast_exp2(x.x);
+            pf[j + 1] = fast_exp2(x.y);
+          }
         } else {
 #pragma unroll
           for (int j = 0; j < 64; ++j)
@@ -275,9 +280,10 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         uint32_t dw[32];
 #pragma unroll
         for (int j = 0; j < 64; j += 2) {
-          const float d0 = pf[j] * fmaf(__uint_as_float(du[j >> 5][j & 31]), p.sm_scale, ndsc);
-          const float d1 = pf[j + 1] * fmaf(__uint_as_float(du[(j + 1) >> 5][(j + 1) & 31]), p.sm_scale, ndsc);
-          dw[j >> 1] = DT<T>::pack(d0, d1);
+          const float2 t2 = ffma2(make_float2(__uint_as_float(du[j >> 5][j & 31]), __uint_as_float(du[j >> 5][(j & 31) + 1])),
+                                  make_float2(p.sm_scale, p.sm_scale), make_float2(ndsc, ndsc));
+          const float2 d2 = fmul2(make_float2(pf[j], pf[j + 1]), t2);
+          dw[j >> 1] = DT<T>::pack(d2.x, d2.y);
         }
         tmem_st32(lane_base + 128 + half * 64, dw);  // over this thread's own dP logits
         tmem_st_wait();
