@@ -263,10 +263,15 @@ dense_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           for (int j4 = 0; j4 < 16; ++j4) {
             const float4 nl = nl4[j4];
             const int j = 4 * j4;
-            pf[j + 0] = fast_exp2(fmaf(__uint_as_float(su[j >> 5][(j + 0) & 31]), p.scale2, nl.x));
-            pf[j + 1] = fast_exp2(fmaf(__uint_as_float(su[j >> 5][(j + 1) & 31]), p.scale2, nl.y));
-            pf[j + 2] = fast_exp2(fmaf(__uint_as_float(su[j >> 5][(j + 2) & 31]), p.scale2, nl.z));
-            pf[j + 3] = fast_exp2(fmaf(__uint_as_float(su[j >> 5][(j + 3) & 31]), p.scale2, nl.w));
+            const float2 sc2 = make_float2(p.scale2, p.scale2);
+            const float2 x01 = ffma2(make_float2(__uint_as_float(su[j >> 5][(j + 0) & 31]), __uint_as_float(su[j >> 5][(j + 1) & 31])), sc2,
+                                     make_float2(nl.x, nl.y));
+            const float2 x23 = ffma2(make_float2(__uint_as_float(su[j >> 5][(j + 2) & 31]), __uint_as_float(su[j >> 5][(j + 3) & 31])), sc2,
+                                     make_float2(nl.z, nl.w));
+            pf[j + 0] = fast_exp2(x01.x);
+            pf[j + 1] = fast_exp2(x01.y);
+            pf[j + 2] = fast_exp2(x23.x);
+            pf[j + 3] = fast_exp2(x23.y);
           }
         } else {
 #pragma unroll
@@ -302,12 +307,15 @@ dense_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         for (int j4 = 0; j4 < 16; ++j4) {
           const float4 dl = dl4[j4];
           const int j = 4 * j4;
-          const float d0 = pf[j + 0] * fmaf(__uint_as_float(du[j >> 5][(j + 0) & 31]), p.sm_scale, -dl.x);
-          const float d1 = pf[j + 1] * fmaf(__uint_as_float(du[j >> 5][(j + 1) & 31]), p.sm_scale, -dl.y);
-          const float d2 = pf[j + 2] * fmaf(__uint_as_float(du[j >> 5][(j + 2) & 31]), p.sm_scale, -dl.z);
-          const float d3 = pf[j + 3] * fmaf(__uint_as_float(du[j >> 5][(j + 3) & 31]), p.sm_scale, -dl.w);
-          pk[2 * j4] = DT<T>::pack(d0, d1);
-          pk[2 * j4 + 1] = DT<T>::pack(d2, d3);
+          const float2 sm2 = make_float2(p.sm_scale, p.sm_scale);
+          const float2 t01 = ffma2(make_float2(__uint_as_float(du[j >> 5][(j + 0) & 31]), __uint_as_float(du[j >> 5][(j + 1) & 31])), sm2,
+                                   make_float2(-dl.x, -dl.y));
+          const float2 t23 = ffma2(make_float2(__uint_as_float(du[j >> 5][(j + 2) & 31]), __uint_as_float(du[j >> 5][(j + 3) & 31])), sm2,
+                                   make_float2(-dl.z, -dl.w));
+          const float2 d01 = fmul2(make_float2(pf[j + 0], pf[j + 1]), t01);
+          const float2 d23 = fmul2(make_float2(pf[j + 2], pf[j + 3]), t23);
+          pk[2 * j4] = DT<T>::pack(d01.x, d01.y);
+          pk[2 * j4 + 1] = DT<T>::pack(d23.x, d23.y);
         }
         tmem_st32(lane_base + 384 + half * 64, pk);
         tmem_st_wait();

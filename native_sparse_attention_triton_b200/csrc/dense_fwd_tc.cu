@@ -224,9 +224,10 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           tmem_ld32(s_base + c * 32, su);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float v = (!MASKED || (c * 32 + j < lim && c * 32 + j >= lo)) ? __uint_as_float(su[j]) : -INFINITY;
-            mx4[j & 3] = fmaxf(mx4[j & 3], v);
+          for (int j = 0; j < 32; j += 2) {
+            const float v0 = (!MASKED || (c * 32 + j < lim && c * 32 + j >= lo)) ? __uint_as_float(su[j]) : -INFINITY;
+            const float v1 = (!MASKED || (c * 32 + j + 1 < lim && c * 32 + j + 1 >= lo)) ? __uint_as_float(su[j + 1]) : -INFINITY;
+            mx4[(j >> 1) & 3] = fmax3(mx4[(j >> 1) & 3], v0, v1);
           }
         }
       };
@@ -248,7 +249,11 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           tmem_ld32(o_base + c * 32, r);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * factor);
+          for (int j = 0; j < 32; j += 2) {
+            const float2 y = fmul2(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), make_float2(factor, factor));
+            r[j] = __float_as_uint(y.x);
+            r[j + 1] = __float_as_uint(y.y);
+          }
           tmem_st32(o_base + c * 32, r);
         }
         tmem_st_wait();
@@ -256,7 +261,7 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       // ---- pass 2: P = exp2(S*scale - m_ref) as 16-bit pairs over the logits: the 32 columns of chunk c become the 16
       // packed columns [16c, 16c+16), which lie inside chunk c/2 -- already consumed when chunk c is written ----
       const float nm = (m_ref == -INFINITY) ? 0.f : -m_ref;
-      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+      float2 ls2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
       auto pass2 = [&](auto masked_tag) {
         constexpr bool MASKED = decltype(masked_tag)::value;
 #pragma unroll
@@ -267,10 +272,11 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           uint32_t pk[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const float x0 = fmaf(__uint_as_float(su[2 * j]), p.scale2, nm), x1 = fmaf(__uint_as_float(su[2 * j + 1]), p.scale2, nm);
-            const float p0 = MASKED ? masked_exp2(c * 32 + 2 * j < lim && c * 32 + 2 * j >= lo, x0) : fast_exp2(x0);
-            const float p1 = MASKED ? masked_exp2(c * 32 + 2 * j + 1 < lim && c * 32 + 2 * j + 1 >= lo, x1) : fast_exp2(x1);
-            ls[j & 3] += p0 + p1;
+            const float2 x = ffma2(make_float2(__uint_as_float(su[2 * j]), __uint_as_float(su[2 * j + 1])), make_float2(p.scale2, p.scale2),
+                                   make_float2(nm, nm));
+            const float p0 = MASKED ? masked_exp2(c * 32 + 2 * j < lim && c * 32 + 2 * j >= lo, x.x) : fast_exp2(x.x);
+            const float p1 = MASKED ? masked_exp2(c * 32 + 2 * j + 1 < lim && c * 32 + 2 * j + 1 >= lo, x.y) : fast_exp2(x.y);
+            ls2[j & 1] = fadd2(ls2[j & 1], make_float2(p0, p1));
             pk[j] = DT<T>::pack(p0, p1);
           }
           tmem_st16(s_base + c * 16, pk);
@@ -278,7 +284,7 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       };
       if (full) pass2(std::false_type{}); else pass2(std::true_type{});
       tmem_st_wait();
-      l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+      l += (ls2[0].x + ls2[0].y) + (ls2[1].x + ls2[1].y);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full + g);

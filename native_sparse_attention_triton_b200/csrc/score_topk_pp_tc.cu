@@ -182,10 +182,15 @@ score_topk_pp_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
           for (int q4 = 0; q4 < GG / 4; ++q4) {
             const int col = tk * GG + q4 * 4;  // within the 64
             const float4 l4 = lse4[(hc * 64 + col) >> 2];
-            e[q4 * 4 + 0] = fast_exp2(fmaf(__uint_as_float(su[col >> 5][(col + 0) & 31]), p.scale2, -l4.x));
-            e[q4 * 4 + 1] = fast_exp2(fmaf(__uint_as_float(su[col >> 5][(col + 1) & 31]), p.scale2, -l4.y));
-            e[q4 * 4 + 2] = fast_exp2(fmaf(__uint_as_float(su[col >> 5][(col + 2) & 31]), p.scale2, -l4.z));
-            e[q4 * 4 + 3] = fast_exp2(fmaf(__uint_as_float(su[col >> 5][(col + 3) & 31]), p.scale2, -l4.w));
+            const float2 sc2 = make_float2(p.scale2, p.scale2);
+            const float2 x01 = ffma2(make_float2(__uint_as_float(su[col >> 5][(col + 0) & 31]), __uint_as_float(su[col >> 5][(col + 1) & 31])),
+                                     sc2, make_float2(-l4.x, -l4.y));
+            const float2 x23 = ffma2(make_float2(__uint_as_float(su[col >> 5][(col + 2) & 31]), __uint_as_float(su[col >> 5][(col + 3) & 31])),
+                                     sc2, make_float2(-l4.z, -l4.w));
+            e[q4 * 4 + 0] = fast_exp2(x01.x);
+            e[q4 * 4 + 1] = fast_exp2(x01.y);
+            e[q4 * 4 + 2] = fast_exp2(x23.x);
+            e[q4 * 4 + 3] = fast_exp2(x23.y);
           }
 #pragma unroll
           for (int w = GG / 2; w >= 1; w >>= 1)

@@ -311,7 +311,12 @@ sparse_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         // tiles every row of the warp sees in full (all but the block on the diagonal) skip the mask instructions
         if (__all_sync(0xffffffffu, lim >= 32)) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) pf[j] = fast_exp2(fmaf(__uint_as_float(su[j]), p.scale2, nlse));
+          for (int j = 0; j < 32; j += 2) {
+            const float2 x = ffma2(make_float2(__uint_as_float(su[j]), __uint_as_float(su[j + 1])), make_float2(p.scale2, p.scale2),
+                                   make_float2(nlse, nlse));
+            pf[j] = fast_exp2(x.x);
+            pf[j + 1] = fast_exp2(x.y);
+          }
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) pf[j] = masked_exp2(j < lim, fmaf(__uint_as_float(su[j]), p.scale2, nlse));
@@ -342,9 +347,10 @@ sparse_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         uint32_t dw[16];
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
-          const float d0 = pf[j] * fmaf(__uint_as_float(du[j]), p.sm_scale, ndsc);
-          const float d1 = pf[j + 1] * fmaf(__uint_as_float(du[j + 1]), p.sm_scale, ndsc);
-          dw[j >> 1] = DT<T>::pack(d0, d1);
+          const float2 t2 = ffma2(make_float2(__uint_as_float(du[j]), __uint_as_float(du[j + 1])), make_float2(p.sm_scale, p.sm_scale),
+                                  make_float2(ndsc, ndsc));
+          const float2 d2 = fmul2(make_float2(pf[j], pf[j + 1]), t2);
+          dw[j >> 1] = DT<T>::pack(d2.x, d2.y);
         }
         if (i > 0) mbar_wait(ds_empty, (i - 1) & 1, p.st);  // dK of the previous tile has read the dS tile
 #pragma unroll
