@@ -247,6 +247,41 @@ def window_microbench(ops, dev, tokens):
                 per_kernel_ms={k_: v_[1] / reps for k_, v_ in kern.items()})
 
 
+def gate_combine_microbench(ops, dev, tokens):
+    """Gated sum of the three branch outputs at the layer's shape (tokens x 64 heads x 128), forward and backward.  HBM-bound:
+    achieved GB/s on the ALGORITHMIC bytes, 4 tensors forward (3 read, 1 written) and 7 backward (4 read, 3 written) plus the
+    gates, 2 bytes per element.  The working set (1 GB per tensor at 65 536 tokens) is far larger than L2."""
+    g = torch.Generator().manual_seed(9)
+    Hq, d = WORKLOAD["Hq"], WORKLOAD["d"]
+    outs = [torch.randn(tokens, Hq, d, generator=g).to(torch.bfloat16).to(dev).requires_grad_(True) for _ in range(3)]
+    gate = torch.rand(tokens, Hq, 3, generator=g).to(torch.bfloat16).to(dev).requires_grad_(True)
+    do = torch.randn(tokens, Hq, d, generator=g).to(torch.bfloat16).to(dev)
+
+    def step():
+        gate.grad = None
+        for o in outs:
+            o.grad = None
+        ops.gate_combine(gate, *outs).backward(do)
+
+    for _ in range(3):
+        step()
+    pkg_lib = sys.modules["native_sparse_attention_triton_b200"]._lib
+    pkg_lib.profile(True)
+    reps = 5
+    for _ in range(reps):
+        step()
+    torch.cuda.synchronize()
+    kern = pkg_lib.profile_collect()
+    pkg_lib.profile(False)
+    tensor_bytes = 2 * tokens * Hq * d
+    gate_bytes = 2 * tokens * Hq * 3
+    res = dict(tokens=tokens)
+    for name, nbytes in (("gate_combine_fwd", 4 * tensor_bytes + gate_bytes), ("gate_combine_bwd", 7 * tensor_bytes + 2 * gate_bytes)):
+        ms = kern[name][1] / reps
+        res[name] = dict(ms=ms, bytes=nbytes, gb_per_s=nbytes / 1e9 / (ms / 1e3))
+    return res
+
+
 def decode_microbench(ops, dev):
     """The three single-token operators on (a) the bandwidth-sized case of the reference's decode self-tests
     (batch 76, cache 8192, 32q/4kv heads, d=128, block 64, top-16, ragged lengths) and (b) the shapes of the
@@ -435,12 +470,17 @@ def main():
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     e2e_ms = float(e2e_t.item())
     status = pkg.device_status()
-    decode = window = None
+    decode = window = combine = None
     if rank == 0 and not args.no_decode:
         del t, t2, sets, host
         torch.cuda.empty_cache()
         decode = decode_microbench(ops, dev)
         window = window_microbench(ops, dev, N)
+        torch.cuda.empty_cache()
+        combine = gate_combine_microbench(ops, dev, N)
+        for v_ in combine.values():
+            if isinstance(v_, dict):
+                v_["frac_of_hbm_peak"] = v_["gb_per_s"] / peaks()["hbm"]
 
     if rank != 0:
         if dist is not None:
@@ -495,7 +535,7 @@ def main():
                          note="host->device copy of step s+1 overlaps the compute of step s (two input sets)"),
                 gpu_launches=launches, roofline=roofline, cpu_baseline=cpu,
                 tokens_per_s=world * N / (ms / 1e3), useful_tflops_per_gpu=useful_tflops,
-                frac_of_tc_peak=useful_tflops / pk["tc_sustained"], per_kernel_ms=per_kernel, kernel_rooflines=kernel_rooflines, decode=decode, sliding_window=window,
+                frac_of_tc_peak=useful_tflops / pk["tc_sustained"], per_kernel_ms=per_kernel, kernel_rooflines=kernel_rooflines, decode=decode, sliding_window=window, gate_combine=combine,
                 hbm_peak_gb_per_s=pk["hbm"], device_status=status)
     print(json.dumps(line), flush=True)
     if dist is not None:

@@ -219,6 +219,25 @@ int nsa_pool_compress_bwd(const void* x, const void* w, const void* pe, const vo
                           int total_len, int batch, int total_y, int num_heads, int head_dim, int kernel_size,
                           int kernel_stride, long long x_stride_n, long long x_stride_h, int dtype, void* stream);
 
+/* Gated sum of the three branch outputs of an NSA layer,
+ *   out[n, h, :] = gate[n, h, 0] * o_cmp[n, h, :] + gate[n, h, 1] * o_sel[n, h, :] + gate[n, h, 2] * o_win[n, h, :],
+ * in one pass with fp32 arithmetic and one rounding.  The reference has no operator for it: its layer evaluates the
+ * expression in eager PyTorch, native_sparse_attention/module/native_sparse_attention.py:226-232 (training / prefill)
+ * and native_sparse_attention/infer/nsa_inference.py:146-150 (prefill and decode; there n is the batch index).
+ *   gate [total_len, num_heads, 3] (the three gates of a head contiguous), o_* and out [total_len, num_heads, head_dim];
+ *   strides[10] in elements = {gate_n, gate_h, cmp_n, cmp_h, sel_n, sel_h, win_n, win_h, out_n, out_h}; the head_dim axis is
+ *   contiguous, row strides of o_* and out multiples of 8, base pointers 16-byte aligned.  head_dim 64 or 128. */
+int nsa_gate_combine_fwd(const void* gate, const void* o_cmp, const void* o_sel, const void* o_win, void* out, int total_len,
+                         int num_heads, int head_dim, const long long* strides, int dtype, void* stream);
+
+/* Backward of nsa_gate_combine_fwd: d_o_i = gate_i * dout, d_gate[n, h, i] = sum_d dout[n, h, d] * o_i[n, h, d] (fp32 sum in a
+ * fixed order, rounded once).  Replaces the autograd graph of the same expression (three multiplies, two adds).
+ *   strides[18] = {gate_n, gate_h, cmp_n, cmp_h, sel_n, sel_h, win_n, win_h, dout_n, dout_h, dgate_n, dgate_h,
+ *                  dcmp_n, dcmp_h, dsel_n, dsel_h, dwin_n, dwin_h}. */
+int nsa_gate_combine_bwd(const void* gate, const void* o_cmp, const void* o_sel, const void* o_win, const void* dout,
+                         void* d_gate, void* d_cmp, void* d_sel, void* d_win, int total_len, int num_heads, int head_dim,
+                         const long long* strides, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -469,3 +469,12 @@ def total_useful_flops(seqlens, Hq, Hkv, d, kernel_size, kernel_stride, block_si
     if not backward:
         return fwd
     return fwd + 2.5 * (f["cmp_fwd"] + f["sel_fwd"]) + 2.0 * f["lin_fwd"]
+
+
+def gate_combine(gate, o_cmp, o_sel, o_win):
+    """Gated sum of the three branch outputs, gate [n, h, 3], o_* [n, h, d]: the expression of the reference's layer
+    (native_sparse_attention/module/native_sparse_attention.py:226-232, infer/nsa_inference.py:146-150) evaluated in fp32.
+    No test of the reference pins this step (its layer scripts only run); parity unpinned beyond the expression itself."""
+    g = gate.float()
+    out = g[..., 0:1] * o_cmp.float() + g[..., 1:2] * o_sel.float() + g[..., 2:3] * o_win.float()
+    return out.to(o_cmp.dtype)
