@@ -282,6 +282,29 @@ def gate_combine_microbench(ops, dev, tokens):
     return res
 
 
+def rope_microbench(ops, dev, tokens):
+    """Rotary embedding of the query tensor at the layer's shape (tokens x 64 heads x 128), forward only (the backward pass
+    is the same kernel with the opposite angle).  HBM-bound: one read and one write of the tensor, 2 bytes per element."""
+    g = torch.Generator().manual_seed(10)
+    Hq, d = WORKLOAD["Hq"], WORKLOAD["d"]
+    x = torch.randn(tokens, Hq, d, generator=g).to(torch.bfloat16).to(dev)
+    inv_freq = (1.0 / (500000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(dev)
+    cu = torch.tensor([0, tokens], dtype=torch.int32, device=dev)
+    for _ in range(3):
+        ops.rope(x, inv_freq, cu)
+    pkg_lib = sys.modules["native_sparse_attention_triton_b200"]._lib
+    pkg_lib.profile(True)
+    reps = 5
+    for _ in range(reps):
+        ops.rope(x, inv_freq, cu)
+    torch.cuda.synchronize()
+    kern = pkg_lib.profile_collect()
+    pkg_lib.profile(False)
+    nbytes = 2 * 2 * tokens * Hq * d
+    ms = kern["rope"][1] / reps
+    return dict(tokens=tokens, ms=ms, bytes=nbytes, gb_per_s=nbytes / 1e9 / (ms / 1e3))
+
+
 def decode_microbench(ops, dev):
     """The three single-token operators on (a) the bandwidth-sized case of the reference's decode self-tests
     (batch 76, cache 8192, 32q/4kv heads, d=128, block 64, top-16, ragged lengths) and (b) the shapes of the
@@ -470,7 +493,7 @@ def main():
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     e2e_ms = float(e2e_t.item())
     status = pkg.device_status()
-    decode = window = combine = None
+    decode = window = combine = rope = None
     if rank == 0 and not args.no_decode:
         del t, t2, sets, host
         torch.cuda.empty_cache()
@@ -478,6 +501,9 @@ def main():
         window = window_microbench(ops, dev, N)
         torch.cuda.empty_cache()
         combine = gate_combine_microbench(ops, dev, N)
+        torch.cuda.empty_cache()
+        rope = rope_microbench(ops, dev, N)
+        rope["frac_of_hbm_peak"] = rope["gb_per_s"] / peaks()["hbm"]
         for v_ in combine.values():
             if isinstance(v_, dict):
                 v_["frac_of_hbm_peak"] = v_["gb_per_s"] / peaks()["hbm"]
@@ -535,7 +561,7 @@ def main():
                          note="host->device copy of step s+1 overlaps the compute of step s (two input sets)"),
                 gpu_launches=launches, roofline=roofline, cpu_baseline=cpu,
                 tokens_per_s=world * N / (ms / 1e3), useful_tflops_per_gpu=useful_tflops,
-                frac_of_tc_peak=useful_tflops / pk["tc_sustained"], per_kernel_ms=per_kernel, kernel_rooflines=kernel_rooflines, decode=decode, sliding_window=window, gate_combine=combine,
+                frac_of_tc_peak=useful_tflops / pk["tc_sustained"], per_kernel_ms=per_kernel, kernel_rooflines=kernel_rooflines, decode=decode, sliding_window=window, gate_combine=combine, rope=rope,
                 hbm_peak_gb_per_s=pk["hbm"], device_status=status)
     print(json.dumps(line), flush=True)
     if dist is not None:

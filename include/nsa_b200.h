@@ -238,6 +238,20 @@ int nsa_gate_combine_bwd(const void* gate, const void* o_cmp, const void* o_sel,
                          void* d_gate, void* d_cmp, void* d_sel, void* d_win, int total_len, int num_heads, int head_dim,
                          const long long* strides, int dtype, void* stream);
 
+/* Rotary position embedding of a varlen batch, y = x * cos + rotate_half(x) * sin, positions taken from cu_seqlens on the
+ * device.  Replaces RotaryEmbedding.forward with generate_pos_embs / generate_cos_sin (a Python loop over the batch, table
+ * slices, three elementwise passes and a concatenation), native_sparse_attention/module/rope.py:36-41,126-155,158-209;
+ * call sites module/native_sparse_attention.py:180-183,205 and infer/nsa_inference.py:94-103.
+ *   x, y [total_rows, num_heads, head_dim] (strides in elements; y may be x); inv_freq fp32 [head_dim / 2] (from the
+ *   caller's frequency initialiser); angle = inv_freq[j] * position in fp32; cos and sin are multiplied by
+ *   attention_scaling and rounded to the tensor's dtype as the reference's tables are, the rotation itself runs in fp32.
+ *   step == 0 (prefill / training): row n, the t-th token of its sequence, has position t * stride.
+ *   step  > 0 (decode): total_rows == batch and row b has position (cu_seqlens[b+1] - cu_seqlens[b] + step - 1) * stride.
+ *   inverse != 0 rotates by the opposite angle: the backward pass (dx from dy).  head_dim 64 or 128. */
+int nsa_rope(const void* x, void* y, const float* inv_freq, const int* cu_seqlens, int total_rows, int batch, int num_heads,
+             int head_dim, int step, int stride, float attention_scaling, int inverse, long long x_stride_n,
+             long long x_stride_h, long long y_stride_n, long long y_stride_h, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -478,3 +478,26 @@ def gate_combine(gate, o_cmp, o_sel, o_win):
     g = gate.float()
     out = g[..., 0:1] * o_cmp.float() + g[..., 1:2] * o_sel.float() + g[..., 2:3] * o_win.float()
     return out.to(o_cmp.dtype)
+
+
+def rope(x, inv_freq, cu_seqlens, step=0, stride=1, attention_scaling=1.0):
+    """Rotary embedding of a varlen batch, x [rows, heads, d]: x * cos + rotate_half(x) * sin with rotate_half(x) =
+    cat(-x2, x1) (native_sparse_attention/module/rope.py:36-41,204-209); cos/sin of the fp32 angle inv_freq * position,
+    times attention_scaling, rounded to x.dtype (:126-155); position t * stride for the t-th token of a sequence when
+    step == 0, (seqlen_b + step - 1) * stride for row b when step > 0 (:158-195).  The arithmetic after the table lookup is
+    fp32 here (the reference rounds each product to x.dtype).  The reference's module cannot be imported without a GPU
+    (rope.py:74 calls torch.cuda.current_device() in a default argument) and its tests hold no vectors for it: parity
+    unpinned beyond this restatement."""
+    lens = (cu_seqlens[1:] - cu_seqlens[:-1]).tolist()
+    if step == 0:
+        pos = torch.cat([torch.arange(n) for n in lens]) if lens else torch.zeros(0, dtype=torch.long)
+    else:
+        pos = torch.tensor([n + step - 1 for n in lens])
+    pos = (pos * stride).float()
+    ang = inv_freq.float()[None, :] * pos[:, None]
+    cos = (ang.cos() * attention_scaling).to(x.dtype).float()
+    sin = (ang.sin() * attention_scaling).to(x.dtype).float()
+    half = x.shape[-1] // 2
+    x1, x2 = x[..., :half].float(), x[..., half:].float()
+    c, s = cos[:, None, :], sin[:, None, :]
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1).to(x.dtype)
