@@ -252,6 +252,49 @@ int nsa_rope(const void* x, void* y, const float* inv_freq, const int* cu_seqlen
              int head_dim, int step, int stride, float attention_scaling, int inverse, long long x_stride_n,
              long long x_stride_h, long long y_stride_n, long long y_stride_h, int dtype, void* stream);
 
+/* ---- KV-cache maintenance of NSA inference (device-side counters, no host synchronisation) ----
+ * Replace NSACache.prepare_compress / update_kv and _fill_kv_cache, native_sparse_attention/module/kv_cache.py:233-449,
+ * 452-555 (a Triton copy kernel sized by .max().item(), and about twenty indexing launches per decode step).
+ * Every cache is [2 (key, value)][max_batch][rows][heads][head_dim] of 16-bit elements; cache strides are
+ * {kv, batch, row, head} in elements, head_dim contiguous, all strides multiples of 8, bases 16-byte aligned; counters are
+ * int32 [max_batch].  A row that does not fit is dropped and bit 2 (bad index) of the device status word is raised. */
+
+/* Prefill: copy rows of a varlen batch into a cache and set its counters (row t of the kept part goes to cache row t).
+ *   mode 0: whole sequences (selected-block cache; compressed cache, with the compressed tokens and their cu_seqlens);
+ *   mode 1: the last `window` rows of each sequence (sliding-window ring), kv_cache.py:381-391;
+ *   mode 2: the rows after the last full compression hop, window = kernel_size, hop = kernel_stride (staging buffer of
+ *           tokens the next compressed token needs), kv_cache.py:266-276.
+ *   strides[8] = {cache_kv, cache_b, cache_row, cache_h, key_n, key_h, value_n, value_h}. */
+int nsa_kv_cache_fill(void* cache, int* cache_len, const void* key, const void* value, const int* cu_seqlens, int mode,
+                      int window, int hop, int total_rows, int batch, int cache_rows, int num_heads, int head_dim,
+                      const long long* strides, void* stream);
+
+/* Decode, before compression (_prepare_compress_decode, kv_cache.py:278-307): staging buffers that are full drop their
+ * first kernel_stride rows, then every sequence appends its new key/value row [batch, heads, head_dim].
+ *   strides[8] as above (key_n / value_n = stride between sequences). */
+int nsa_kv_cache_stage_decode(void* stage_cache, int* stage_len, const void* key, const void* value, int batch,
+                              int kernel_size, int kernel_stride, int num_heads, int head_dim, const long long* strides,
+                              void* stream);
+
+/* Decode, after compression and rotary embedding (_update_kv_decode, kv_cache.py:393-449): append the compressed token
+ * of every sequence whose staging buffer is full (stage_len[b] == kernel_size), the new token to the selected-block cache,
+ * and the new token to the sliding-window ring at slot count % sliding_rows; bump the three counters.
+ *   strides[24] = {compress cache kv, b, row, h; sparse cache ...; sliding cache ...; then (n, h) of compress_key,
+ *   compress_value, sparse_key, sparse_value, sliding_key, sliding_value}. */
+int nsa_kv_cache_append_decode(void* compress_cache, int* compress_len, void* sparse_cache, int* sparse_len,
+                               void* sliding_cache, int* sliding_len, const int* stage_len, const void* compress_key,
+                               const void* compress_value, const void* sparse_key, const void* sparse_value,
+                               const void* sliding_key, const void* sliding_value, int batch, int kernel_size,
+                               int compress_rows, int sparse_rows, int sliding_rows, int num_heads, int head_dim,
+                               const long long* strides, void* stream);
+
+/* Rotary embedding of one decode row per sequence at a position read from the device: row b sits at lengths[b] * stride
+ * (lengths = a cache counter BEFORE the new token is appended), so that a decode step does not depend on a host-side step
+ * number and can be replayed from a CUDA graph.  Otherwise as nsa_rope. */
+int nsa_rope_decode(const void* x, void* y, const float* inv_freq, const int* lengths, int batch, int num_heads, int head_dim,
+                    int stride, float attention_scaling, int inverse, long long x_stride_n, long long x_stride_h,
+                    long long y_stride_n, long long y_stride_h, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

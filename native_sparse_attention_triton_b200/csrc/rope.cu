@@ -21,7 +21,7 @@ struct RopeParams {
   const void* x;
   void* y;
   const float* inv_freq;  // [D / 2]
-  const int* cu;          // [B + 1]
+  const int* cu;          // [B + 1] cu_seqlens, or [B] lengths when step < 0
   long long x_sn, x_sh, y_sn, y_sh;
   int N, B, H, step, stride, inverse;
   float scaling;
@@ -48,8 +48,10 @@ __global__ void __launch_bounds__(256) rope_kernel(RopeParams p) {
         if (p.step == 0) {
           const int b = find_sequence(p.cu, p.B, n);
           pos = (n - __ldg(p.cu + b)) * p.stride;
-        } else {
+        } else if (p.step > 0) {
           pos = (__ldg(p.cu + n + 1) - __ldg(p.cu + n) + p.step - 1) * p.stride;
+        } else {  // decode row at a length counter read from the device
+          pos = __ldg(p.cu + n) * p.stride;
         }
         float s, c;
         sincosf(__ldg(p.inv_freq + j) * (float)pos, &s, &c);
@@ -114,6 +116,21 @@ extern "C" int nsa_rope(const void* x, void* y, const float* inv_freq, const int
   p.x = x; p.y = y; p.inv_freq = inv_freq; p.cu = cu_seqlens;
   p.x_sn = x_stride_n; p.x_sh = x_stride_h; p.y_sn = y_stride_n; p.y_sh = y_stride_h;
   p.N = total_rows; p.B = batch; p.H = num_heads; p.step = step; p.stride = stride; p.inverse = inverse ? 1 : 0;
+  p.scaling = attention_scaling;
+  return NSA_DISPATCH_T_D(dtype, head_dim, launch_rope, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nsa_rope_decode(const void* x, void* y, const float* inv_freq, const int* lengths, int batch, int num_heads,
+                               int head_dim, int stride, float attention_scaling, int inverse, long long x_stride_n,
+                               long long x_stride_h, long long y_stride_n, long long y_stride_h, int dtype, void* stream) {
+  using namespace nsa;
+  if (!inv_freq || !lengths || batch <= 0 || num_heads <= 0 || stride <= 0) return kInvalid;
+  if (!x || !y || !aligned16(x) || !aligned16(y)) return kInvalid;
+  if ((x_stride_n | x_stride_h | y_stride_n | y_stride_h) % 8) return kInvalid;
+  RopeParams p;
+  p.x = x; p.y = y; p.inv_freq = inv_freq; p.cu = lengths;
+  p.x_sn = x_stride_n; p.x_sh = x_stride_h; p.y_sn = y_stride_n; p.y_sh = y_stride_h;
+  p.N = batch; p.B = batch; p.H = num_heads; p.step = -1; p.stride = stride; p.inverse = inverse ? 1 : 0;
   p.scaling = attention_scaling;
   return NSA_DISPATCH_T_D(dtype, head_dim, launch_rope, p, static_cast<cudaStream_t>(stream));
 }

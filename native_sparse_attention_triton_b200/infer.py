@@ -1,0 +1,168 @@
+"""NSA inference step (prefill and decode) on the library's kernels, with a decode step free of host synchronisation.
+
+``nsa_infer`` has the signature and the order of operations of the reference's
+native_sparse_attention/infer/nsa_inference.py:24-152 (with its helpers infer/inference_func.py:27-202): stage tokens for
+compression, compress, rotary embedding of query / compressed key / key, cache update, the three attention branches, the
+gated sum.  Differences, all on the decode path: positions and lengths come from the cache's device counters instead of
+the host-side ``step`` number, the staging buffers are compressed through the C interface with precomputed cu_seqlens,
+the compressed cache is passed whole (lengths mask it) instead of sliced to ``.max()``, and the sliding-window length is
+clamped on the device -- so one decode step is a fixed sequence of launches that ``DecodeGraph`` captures once and replays.
+"""
+from typing import Callable, Optional, Tuple
+
+import torch
+
+from . import _lib
+from . import ops
+from .kv_cache import NSACache
+from .ops._common import dtype_code, inner_contiguous, ptr, stream_ptr
+
+
+class RotaryEmbedding:
+    """Callable with the reference module's call signature, ``rope(x, cu_seqlens, step=0, stride=1)``
+    (native_sparse_attention/module/rope.py:197-209), on ``ops.rope``; the frequencies are the caller's."""
+
+    def __init__(self, inv_freq: torch.Tensor, attention_scaling: float = 1.0):
+        assert inv_freq.dtype == torch.float32 and inv_freq.dim() == 1
+        self.inv_freq = inv_freq.contiguous()
+        self.attention_scaling = float(attention_scaling)
+
+    def __call__(self, x, cu_seqlens, step: int = 0, stride: int = 1):
+        return ops.rope(x, self.inv_freq, cu_seqlens, step, stride, self.attention_scaling)
+
+    def decode_at(self, x: torch.Tensor, lengths: torch.Tensor, stride: int = 1) -> torch.Tensor:
+        """Row b of x [batch, heads, d] rotated to position lengths[b] * stride, read on the device."""
+        x = inner_contiguous(x)
+        y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        batch, num_heads, head_dim = x.shape
+        assert lengths.dtype == torch.int32 and lengths.shape[0] >= batch
+        torch.cuda.set_device(x.device)
+        rc = _lib.lib().nsa_rope_decode(ptr(x), ptr(y), ptr(self.inv_freq), ptr(lengths), batch, num_heads, head_dim, int(stride),
+                                        self.attention_scaling, 0, x.stride(0), x.stride(1), y.stride(0), y.stride(1),
+                                        dtype_code(x), stream_ptr(x.device))
+        _lib.check(rc, "nsa_rope_decode")
+        return y
+
+
+def _compress_staged(cache: NSACache, batch: int, which: int, func: Callable, weight, pe):
+    """One compressed row per sequence from the staging buffers [batch * kernel_size, heads, d] (the reference runs its
+    compress function over them with an arange cu_seqlens, infer/inference_func.py:56-87).  The library's own compress
+    functions go through the C interface directly (no host copy of cu_seqlens); any other callable is called as given."""
+    x = cache.before_compress_kv_cache[which, :batch].view(batch * cache.kernel_size, cache.num_kv_heads, cache.head_dim)
+    cu, ycu = cache.stage_cu_seqlens[:batch + 1], cache.stage_out_cu_seqlens[:batch + 1]
+    mode = {ops.linear_compress: "linear", ops.weightedpool_compress: "weighted", ops.avgpool_compress: "avg"}.get(func)
+    if mode is None:
+        return func(x, weight, cu, cache.kernel_size, cache.kernel_stride, pe)[0]
+    y = torch.empty(batch, cache.num_kv_heads, cache.head_dim, dtype=x.dtype, device=x.device)
+    bias = torch.empty(cache.num_kv_heads, cache.head_dim, dtype=x.dtype, device=x.device) if pe is not None else None
+    w = weight.contiguous() if weight is not None else None
+    pec = pe.contiguous() if pe is not None else None
+    lib = _lib.lib()
+    torch.cuda.set_device(x.device)
+    if mode == "linear":
+        rc = lib.nsa_linear_compress_fwd(ptr(x), ptr(w), ptr(pec), ptr(cu), ptr(ycu), ptr(y), ptr(bias), batch, batch, 1,
+                                         cache.num_kv_heads, cache.head_dim, cache.kernel_size, cache.kernel_stride, x.stride(0),
+                                         x.stride(1), dtype_code(x), stream_ptr(x.device))
+        _lib.check(rc, "nsa_linear_compress_fwd")
+    else:
+        rc = lib.nsa_pool_compress_fwd(ptr(x), ptr(w), ptr(pec), ptr(cu), ptr(ycu), ptr(y), ptr(bias), batch, batch,
+                                       cache.num_kv_heads, cache.head_dim, cache.kernel_size, cache.kernel_stride, x.stride(0),
+                                       x.stride(1), dtype_code(x), stream_ptr(x.device))
+        _lib.check(rc, "nsa_pool_compress_fwd")
+    return y
+
+
+@torch.no_grad()
+def nsa_infer(cu_seqlens: torch.Tensor, step: int, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+              gate_value: torch.Tensor, rope, cache: NSACache, compress_weight: Tuple[torch.Tensor, torch.Tensor],
+              compress_func: Tuple[Callable, Callable], intra_block_pe: Optional[torch.Tensor], kernel_size: int,
+              kernel_stride: int, block_size: int, topk: int, init_blocks: int, local_blocks: int,
+              window_size: int) -> torch.Tensor:
+    """Prefill (step == 0; query/key/value [total_len, heads, d]) or one decode step (step > 0; [batch, heads, d]).
+    cu_seqlens always describes the PREFILL batch; gate_value is [rows, q_heads, 3].  Returns the gated attention output
+    with the shape of query."""
+    assert kernel_size == cache.kernel_size and kernel_stride == cache.kernel_stride and window_size == cache.window_size
+    batch = cu_seqlens.shape[0] - 1
+    if step == 0:
+        cache.reset()
+        cache.prepare_compress(cu_seqlens, 0, key, value)
+        compress_key, compress_cu_seqlens = compress_func[0](key, compress_weight[0], cu_seqlens, kernel_size, kernel_stride,
+                                                             intra_block_pe)
+        compress_value, _ = compress_func[1](value, compress_weight[1], cu_seqlens, kernel_size, kernel_stride)
+        query = rope(query, cu_seqlens, 0)
+        compress_key = rope(compress_key, compress_cu_seqlens, 0, stride=kernel_stride)
+        key = rope(key, cu_seqlens, 0)
+        cache.update_kv(cu_seqlens, 0, compress_key, compress_value, key, value, key, value, compress_cu_seqlens)
+        seqlens = cu_seqlens[1:] - cu_seqlens[:-1]
+        compress_seqlens = compress_cu_seqlens[1:] - compress_cu_seqlens[:-1]
+        max_len, max_comp = int(seqlens.max().item()), int(compress_seqlens.max().item())
+        o_cmp, topk_idx = ops.compressed_attention(query, compress_key, compress_value, kernel_size, kernel_stride, block_size,
+                                                   topk, cu_seqlens, compress_cu_seqlens, max_len, max_comp, None, init_blocks,
+                                                   local_blocks)
+        o_sel = ops.topk_sparse_attention(query, key, value, topk_idx, block_size, cu_seqlens)
+        o_win = ops.sliding_window_attention(query, key, value, cu_seqlens, max_len, window_size)
+        return ops.gate_combine(gate_value, o_cmp, o_sel, o_win)
+
+    # ---- decode: nothing below reads a device value on the host ----
+    cache.prepare_compress(cu_seqlens, step, key, value)
+    compress_key = _compress_staged(cache, batch, 0, compress_func[0], compress_weight[0], intra_block_pe)
+    compress_value = _compress_staged(cache, batch, 1, compress_func[1], compress_weight[1], None)
+    if hasattr(rope, "decode_at"):
+        # the new token's index is the number of tokens cached so far; the compressed token's, the compressed count
+        query = rope.decode_at(query, cache.sparse_kv_len, 1)
+        key = rope.decode_at(key, cache.sparse_kv_len, 1)
+        compress_key = rope.decode_at(compress_key, cache.compress_kv_len, kernel_stride)
+    else:
+        compress_cu = torch.zeros(batch + 1, dtype=torch.int32, device=key.device)
+        compress_cu[1:] = torch.cumsum(cache.compress_kv_len[:batch], 0)
+        query = rope(query, cu_seqlens, step)
+        compress_key = rope(compress_key, compress_cu, 1, stride=kernel_stride)
+        key = rope(key, cu_seqlens, step)
+    cache.update_kv(cu_seqlens, step, compress_key, compress_value, key, value, key, value)
+    seqlens = cache.sparse_kv_len[:batch]  # counts the new token
+    o_cmp, topk_idx = ops.compressed_attention_decode(query, cache.compress_kv_cache[0, :batch], cache.compress_kv_cache[1, :batch],
+                                                      seqlens, cache.compress_kv_len[:batch], kernel_size, kernel_stride,
+                                                      block_size, topk, init_blocks, local_blocks, max_seqlen=cache.max_length)
+    o_sel = ops.topk_sparse_attention_decode(query, cache.sparse_kv_cache[0, :batch], cache.sparse_kv_cache[1, :batch], topk_idx,
+                                             block_size, seqlens)
+    o_win = ops.flash_attention_decode(query, cache.sliding_kv_cache[0, :batch], cache.sliding_kv_cache[1, :batch],
+                                       torch.clamp(cache.sliding_kv_len[:batch], max=window_size))
+    return ops.gate_combine(gate_value, o_cmp, o_sel, o_win)
+
+
+class DecodeGraph:
+    """One decode step of ``nsa_infer`` captured in a CUDA graph: ``graph(query, key, value, gate_value)`` copies the four
+    inputs into fixed buffers, replays the launches and returns the (fixed) output tensor.  Capture after prefill; the
+    cache object, weights and shapes are fixed at capture."""
+
+    def __init__(self, cu_seqlens, query, key, value, gate_value, **nsa_args):
+        self.inputs = [t.clone() for t in (query, key, value, gate_value)]
+        self.args = dict(nsa_args)
+        self.cu_seqlens = cu_seqlens
+        cache: NSACache = nsa_args["cache"]
+        # The warm-up step below (which also performs every lazy one-time initialisation of the library outside the capture)
+        # and the capture itself both advance the cache: snapshot its state and restore it afterwards.
+        state = [t.clone() for t in self._state(cache)]
+        side = torch.cuda.Stream(device=query.device)
+        side.wait_stream(torch.cuda.current_stream(query.device))
+        with torch.cuda.stream(side):
+            nsa_infer(cu_seqlens, 1, *self.inputs, **self.args)
+        torch.cuda.current_stream(query.device).wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.output = nsa_infer(cu_seqlens, 1, *self.inputs, **self.args)
+        for dst, src in zip(self._state(cache), state):
+            dst.copy_(src)
+
+    @staticmethod
+    def _state(cache):
+        # what a step overwrites: the counters, the staging buffers (shifted) and the ring (a live slot once it is full);
+        # rows appended to the two large caches lie beyond the restored counters and are rewritten by the next real step
+        return (cache.sparse_kv_len, cache.compress_kv_len, cache.before_compress_kv_cache, cache.before_compress_kv_len,
+                cache.sliding_kv_cache, cache.sliding_kv_len)
+
+    def __call__(self, query, key, value, gate_value):
+        for dst, src in zip(self.inputs, (query, key, value, gate_value)):
+            dst.copy_(src)
+        self.graph.replay()
+        return self.output

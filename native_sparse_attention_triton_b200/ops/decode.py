@@ -94,11 +94,14 @@ def topk_sparse_attention_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tens
 def compressed_attention_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seqlens: torch.Tensor,
                                 compress_seqlens: torch.Tensor, kernel_size: int, kernel_stride: int, block_size: int,
                                 topk: int, init_blocks: int = 1, local_blocks: int = 2,
-                                sm_scale: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+                                sm_scale: Optional[float] = None, max_seqlen: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Single-token attention over the compressed cache and block selection for the current token.
 
     seqlens counts the current token; compress_seqlens is the number of valid compressed rows.
     Returns (o [batch, num_q_heads, d], topk_idx int32 [num_kv_heads, batch, min(topk, num_blocks)]).
+    num_blocks = ceil(max(seqlens) / block_size) as in the reference, which costs a device-to-host copy; a caller that must
+    not synchronise passes max_seqlen (an upper bound, e.g. the cache capacity): the width of topk_idx then follows the
+    bound and the entries beyond a sequence's blocks are -1.
     """
     assert block_size % kernel_size == 0 and kernel_size % kernel_stride == 0
     require_cuda(q, k, v, seqlens, compress_seqlens)
@@ -111,7 +114,8 @@ def compressed_attention_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
     compress_seqlens = compress_seqlens.to(torch.int32)
     if sm_scale is None:
         sm_scale = default_scale(head_dim)
-    max_seqlen = int(seqlens.max().item())
+    if max_seqlen is None:
+        max_seqlen = int(seqlens.max().item())
     max_blocks = (max_seqlen + block_size - 1) // block_size
     t_out = min(topk, max_blocks)
     o = torch.empty_like(q)

@@ -501,3 +501,54 @@ def rope(x, inv_freq, cu_seqlens, step=0, stride=1, attention_scaling=1.0):
     x1, x2 = x[..., :half].float(), x[..., half:].float()
     c, s = cos[:, None, :], sin[:, None, :]
     return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1).to(x.dtype)
+
+
+# --------------------------------------------------------------------------- #
+# inference step (cache bookkeeping restated as a function of the token history)
+# --------------------------------------------------------------------------- #
+def nsa_decode_token(q_new, k_hist, v_hist, gate_new, inv_freq, compress_k, compress_v, w_k, w_v, pe, kernel_size,
+                     kernel_stride, block_size, topk, init_blocks, local_blocks, window_size, attention_scaling=1.0):
+    """Output of one decode step of the reference's NSA inference for ONE sequence, as a function of its history:
+    q_new [Hq, d], gate_new [Hq, 3] belong to the newest token; k_hist, v_hist [n, Hkv, d] are the keys/values of all n
+    tokens including it, BEFORE rotary embedding.  compress_k / compress_v are the oracle's compress functions.
+
+    What the reference's caches hold at that moment (native_sparse_attention/module/kv_cache.py:233-449, driven by
+    infer/nsa_inference.py:77-150 and infer/inference_func.py:27-202) is determined by n alone:
+      * its staging buffer is compressed whenever it holds kernel_size tokens and then drops kernel_stride of them, so the
+        compressed cache holds the windows [i*stride, i*stride + kernel_size) that fit in n tokens -- the same
+        (n - kernel_size) // stride + 1 windows a prefill of n tokens gives -- compressed before rotary embedding, the keys
+        then rotated to position i * stride;
+      * the selected-block cache holds all n rotated keys and the values; the query is rotated to position n - 1;
+      * the sliding-window ring holds the last min(n, window_size) tokens (one fewer than a prefill row sees).
+    """
+    n = k_hist.shape[0]
+    cu = torch.tensor([0, n], dtype=torch.int32)
+    ck, cu_c = compress_k(k_hist, w_k, cu, kernel_size, kernel_stride, pe)
+    cv, _ = compress_v(v_hist, w_v, cu, kernel_size, kernel_stride, None)
+    m = ck.shape[0]
+    q_r = rope(q_new[None], inv_freq, torch.tensor([0, n - 1], dtype=torch.int32), 1, 1, attention_scaling)  # position n - 1
+    k_r = rope(k_hist, inv_freq, cu, 0, 1, attention_scaling)
+    ck_r = rope(ck, inv_freq, cu_c, 0, kernel_stride, attention_scaling) if m > 0 else ck
+    lens, clens = torch.tensor([n], dtype=torch.int32), torch.tensor([m], dtype=torch.int32)
+    o_cmp, idx = compressed_attention_decode(q_r, ck_r[None], cv[None], lens, clens, kernel_size, kernel_stride, block_size,
+                                             topk, init_blocks, local_blocks)
+    o_sel = topk_sparse_attention_decode(q_r, k_r[None], v_hist[None], idx, block_size, lens)
+    w = min(n, window_size)
+    o_win = flash_attention_decode(q_r, k_r[None, n - w:], v_hist[None, n - w:], torch.tensor([w], dtype=torch.int32))
+    return gate_combine(gate_new[None], o_cmp, o_sel, o_win)[0]
+
+
+def nsa_prefill(q, k, v, gate, cu_seqlens, inv_freq, compress_k, compress_v, w_k, w_v, pe, kernel_size, kernel_stride,
+                block_size, topk, init_blocks, local_blocks, window_size, attention_scaling=1.0):
+    """Prefill step of the reference's NSA inference (infer/nsa_inference.py:77-150 with step == 0): compression before
+    rotary embedding, rotation of query / compressed key (positions i * stride) / key, the three branches, the gated sum."""
+    ck, cu_c = compress_k(k, w_k, cu_seqlens, kernel_size, kernel_stride, pe)
+    cv, _ = compress_v(v, w_v, cu_seqlens, kernel_size, kernel_stride, None)
+    q_r = rope(q, inv_freq, cu_seqlens, 0, 1, attention_scaling)
+    k_r = rope(k, inv_freq, cu_seqlens, 0, 1, attention_scaling)
+    ck_r = rope(ck, inv_freq, cu_c, 0, kernel_stride, attention_scaling)
+    o_cmp, idx = compressed_attention(q_r, ck_r, cv, kernel_size, kernel_stride, block_size, topk, cu_seqlens, cu_c,
+                                      init_blocks=init_blocks, local_blocks=local_blocks)[:2]
+    o_sel = topk_sparse_attention(q_r, k_r, v, idx, block_size, cu_seqlens)
+    o_win = sliding_window_attention(q_r, k_r, v, cu_seqlens, window_size)
+    return gate_combine(gate, o_cmp, o_sel, o_win)
