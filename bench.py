@@ -305,6 +305,60 @@ def rope_microbench(ops, dev, tokens):
     return dict(tokens=tokens, ms=ms, bytes=nbytes, gb_per_s=nbytes / 1e9 / (ms / 1e3))
 
 
+def decode_step_microbench(dev):
+    """One whole decode step of an NSA layer's attention (stage + compress + rotary embedding + cache update + three
+    attention branches + gated sum) at the shapes of the generation config (batch 4, 8192-token context, 32q/2kv heads,
+    d=128, weighted-pool compression, top-8, window 512): launches per step, microseconds per step launched eagerly from
+    Python and replayed from a CUDA graph."""
+    import math as _m
+    from native_sparse_attention_triton_b200.infer import DecodeGraph, RotaryEmbedding, nsa_infer
+    from native_sparse_attention_triton_b200.kv_cache import NSACache
+    pkg = sys.modules["native_sparse_attention_triton_b200"]
+    ops = pkg.ops
+    B, L, Hq, Hkv, d, ks, st, bs, T, W = 4, 8192, 32, 2, 128, 32, 16, 64, 8, 512
+    g = torch.Generator().manual_seed(21)
+    mk = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16).to(dev)
+    cu = torch.arange(B + 1, dtype=torch.int32, device=dev) * L
+    cache = NSACache(B, L + 256, Hkv, d, ks, st, W, torch.bfloat16, dev)
+    rope = RotaryEmbedding((1.0 / (500000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(dev))
+    wk, wv = (torch.rand(Hkv, ks, generator=g) / ks).to(torch.bfloat16).to(dev), (torch.rand(Hkv, ks, generator=g) / ks).to(torch.bfloat16).to(dev)
+    args = dict(rope=rope, cache=cache, compress_weight=(wk, wv), compress_func=(ops.weightedpool_compress, ops.weightedpool_compress),
+                intra_block_pe=None, kernel_size=ks, kernel_stride=st, block_size=bs, topk=T, init_blocks=1, local_blocks=2,
+                window_size=W)
+    nsa_infer(cu, 0, mk(B * L, Hq, d), mk(B * L, Hkv, d), mk(B * L, Hkv, d), torch.rand(B * L, Hq, 3, generator=g).to(torch.bfloat16).to(dev), **args)
+    step_in = [mk(B, Hq, d), mk(B, Hkv, d), mk(B, Hkv, d), torch.rand(B, Hq, 3, generator=g).to(torch.bfloat16).to(dev)]
+    for s_ in range(1, 4):
+        nsa_infer(cu, s_, *step_in, **args)
+    n0 = pkg._lib.launch_count()
+    nsa_infer(cu, 4, *step_in, **args)
+    launches = pkg._lib.launch_count() - n0
+
+    def timed(fn, reps):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps
+
+    reps = 40
+    state = {"s": 5}
+
+    def eager():
+        nsa_infer(cu, state["s"], *step_in, **args)
+        state["s"] += 1
+
+    eager_us = timed(eager, reps)
+    graph = DecodeGraph(cu, *step_in, **args)
+    for _ in range(3):
+        graph(*step_in)
+    graph_us = timed(lambda: graph(*step_in), reps)
+    return dict(batch=B, context=L, library_launches_per_step=launches, eager_us_per_step=eager_us, graph_us_per_step=graph_us,
+                status=pkg.device_status())
+
+
 def decode_microbench(ops, dev):
     """The three single-token operators on (a) the bandwidth-sized case of the reference's decode self-tests
     (batch 76, cache 8192, 32q/4kv heads, d=128, block 64, top-16, ragged lengths) and (b) the shapes of the
@@ -493,7 +547,7 @@ def main():
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     e2e_ms = float(e2e_t.item())
     status = pkg.device_status()
-    decode = window = combine = rope = None
+    decode = window = combine = rope = decode_step = None
     if rank == 0 and not args.no_decode:
         del t, t2, sets, host
         torch.cuda.empty_cache()
@@ -501,6 +555,8 @@ def main():
         window = window_microbench(ops, dev, N)
         torch.cuda.empty_cache()
         combine = gate_combine_microbench(ops, dev, N)
+        torch.cuda.empty_cache()
+        decode_step = decode_step_microbench(dev)
         torch.cuda.empty_cache()
         rope = rope_microbench(ops, dev, N)
         rope["frac_of_hbm_peak"] = rope["gb_per_s"] / peaks()["hbm"]
@@ -561,7 +617,7 @@ def main():
                          note="host->device copy of step s+1 overlaps the compute of step s (two input sets)"),
                 gpu_launches=launches, roofline=roofline, cpu_baseline=cpu,
                 tokens_per_s=world * N / (ms / 1e3), useful_tflops_per_gpu=useful_tflops,
-                frac_of_tc_peak=useful_tflops / pk["tc_sustained"], per_kernel_ms=per_kernel, kernel_rooflines=kernel_rooflines, decode=decode, sliding_window=window, gate_combine=combine, rope=rope,
+                frac_of_tc_peak=useful_tflops / pk["tc_sustained"], per_kernel_ms=per_kernel, kernel_rooflines=kernel_rooflines, decode=decode, sliding_window=window, gate_combine=combine, rope=rope, decode_step=decode_step,
                 hbm_peak_gb_per_s=pk["hbm"], device_status=status)
     print(json.dumps(line), flush=True)
     if dist is not None:
