@@ -111,5 +111,25 @@ def install_sliding_window():
     return patched
 
 
+def install_inference():
+    """Opt-in: bind the reference's names ``nsa_infer`` and ``NSACache`` (native_sparse_attention/infer/nsa_inference.py:24,
+    module/kv_cache.py:128), wherever its already-imported modules hold them, to this package's device-side cache and
+    host-sync-free decode step.  A cache must then be constructed after this call (the two implementations do not share
+    objects).  Returns the number of bindings replaced."""
+    from .infer import nsa_infer
+    from .kv_cache import NSACache
+    mine = {"nsa_infer": nsa_infer, "NSACache": NSACache}
+    patched = 0
+    for name, mod in list(sys.modules.items()):
+        if mod is None or not (name == _PKG or name.startswith(_PKG + ".")):
+            continue
+        for attr, obj in mine.items():
+            cur = getattr(mod, attr, None)
+            if cur is not None and cur is not obj and not isinstance(cur, type(sys)):
+                setattr(mod, attr, obj)
+                patched += 1
+    return patched
+
+
 def installed() -> bool:
     return getattr(sys.modules.get(f"{_PKG}.ops"), "__nsa_b200_shim__", False)

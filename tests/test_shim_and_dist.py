@@ -24,6 +24,10 @@ def test_shim_routes_reference_imports(tmp_path, monkeypatch):
         COMPRESS_TYPE_TO_FUNC = {"avgpool": avgpool_compress, "weightedpool": weightedpool_compress, "linear": linear_compress}
         def flash_attn_varlen_func(*args, **kwargs):   # stands in for the third-party function the layer imports
             return ("third party", args, kwargs)
+        def nsa_infer(*args, **kwargs):
+            return "reference nsa_infer"
+        class NSACache:
+            pass
     """))
     monkeypatch.syspath_prepend(str(tmp_path))
     for name in [n for n in sys.modules if n.startswith("native_sparse_attention")]:
@@ -54,6 +58,11 @@ def test_shim_routes_reference_imports(tmp_path, monkeypatch):
     with pytest.raises(RuntimeError, match="no CPU path"):   # head_dim 128, causal, windowed: ours (and ours needs CUDA tensors)
         y = torch.zeros(4, 2, 128, dtype=torch.bfloat16)
         ref_module.flash_attn_varlen_func(y, y, y, cu, cu, 4, 4, causal=True, window_size=(2, -1))
+    # opt-in routing of the inference step and its cache
+    from native_sparse_attention_triton_b200.infer import nsa_infer
+    from native_sparse_attention_triton_b200.kv_cache import NSACache
+    assert shim.install_inference() == 2 and shim.install_inference() == 0
+    assert ref_module.nsa_infer is nsa_infer and ref_module.NSACache is NSACache
     for name in [n for n in sys.modules if n.startswith("native_sparse_attention.") or n == "native_sparse_attention"]:
         monkeypatch.delitem(sys.modules, name)
 
