@@ -26,6 +26,11 @@
 
 namespace nsa {
 
+#ifndef NSA_POLY_EVERY
+#define NSA_POLY_EVERY 2
+#endif
+constexpr int kPolyEvery = NSA_POLY_EVERY;  // one pair of exponentials in kPolyEvery is evaluated as a polynomial
+
 struct DenseFwdTcParams {
   void* o;
   float* lse;  // [Nq, Hq]
@@ -274,8 +279,18 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           for (int j = 0; j < 16; ++j) {
             const float2 x = ffma2(make_float2(__uint_as_float(su[2 * j]), __uint_as_float(su[2 * j + 1])), make_float2(p.scale2, p.scale2),
                                    make_float2(nm, nm));
-            const float p0 = MASKED ? masked_exp2(c * 32 + 2 * j < lim && c * 32 + 2 * j >= lo, x.x) : fast_exp2(x.x);
-            const float p1 = MASKED ? masked_exp2(c * 32 + 2 * j + 1 < lim && c * 32 + 2 * j + 1 >= lo, x.y) : fast_exp2(x.y);
+            float p0, p1;
+            if (MASKED) {
+              p0 = masked_exp2(c * 32 + 2 * j < lim && c * 32 + 2 * j >= lo, x.x);
+              p1 = masked_exp2(c * 32 + 2 * j + 1 < lim && c * 32 + 2 * j + 1 >= lo, x.y);
+            } else if (j % kPolyEvery == kPolyEvery - 1) {  // a share of the exponentials runs on the FMA pipe
+              const float2 e = exp2_poly2(x);
+              p0 = e.x;
+              p1 = e.y;
+            } else {
+              p0 = fast_exp2(x.x);
+              p1 = fast_exp2(x.y);
+            }
             ls2[j & 1] = fadd2(ls2[j & 1], make_float2(p0, p1));
             pk[j] = DT<T>::pack(p0, p1);
           }

@@ -189,8 +189,9 @@ score_topk_pp_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
                                      sc2, make_float2(-l4.z, -l4.w));
             e[q4 * 4 + 0] = fast_exp2(x01.x);
             e[q4 * 4 + 1] = fast_exp2(x01.y);
-            e[q4 * 4 + 2] = fast_exp2(x23.x);
-            e[q4 * 4 + 3] = fast_exp2(x23.y);
+            const float2 e23 = exp2_poly2(x23);  // half of the exponentials on the FMA pipe: the pass is bound by the other unit
+            e[q4 * 4 + 2] = e23.x;
+            e[q4 * 4 + 3] = e23.y;
           }
 #pragma unroll
           for (int w = GG / 2; w >= 1; w >>= 1)
