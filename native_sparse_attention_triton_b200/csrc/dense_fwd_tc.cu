@@ -27,7 +27,7 @@
 namespace nsa {
 
 #ifndef NSA_POLY_EVERY
-#define NSA_POLY_EVERY 2
+#define NSA_POLY_EVERY 3
 #endif
 constexpr int kPolyEvery = NSA_POLY_EVERY;  // one pair of exponentials in kPolyEvery is evaluated as a polynomial
 
