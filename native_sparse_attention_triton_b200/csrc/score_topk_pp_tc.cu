@@ -19,6 +19,11 @@
 
 namespace nsa {
 
+#ifndef NSA_SCORE_POLY_EVERY
+#define NSA_SCORE_POLY_EVERY 2
+#endif
+constexpr int kScorePolyEvery = NSA_SCORE_POLY_EVERY;  // one pair of exponentials in kScorePolyEvery is evaluated as a polynomial
+
 namespace {
 constexpr int kPpKeyTile = 128;
 constexpr int kPpStages = 2;
@@ -187,9 +192,12 @@ score_topk_pp_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
                                      sc2, make_float2(-l4.x, -l4.y));
             const float2 x23 = ffma2(make_float2(__uint_as_float(su[col >> 5][(col + 2) & 31]), __uint_as_float(su[col >> 5][(col + 3) & 31])),
                                      sc2, make_float2(-l4.z, -l4.w));
-            e[q4 * 4 + 0] = fast_exp2(x01.x);
-            e[q4 * 4 + 1] = fast_exp2(x01.y);
-            const float2 e23 = exp2_poly2(x23);  // half of the exponentials on the FMA pipe: the pass is bound by the other unit
+            // a share of the exponentials runs as a polynomial on the FMA pipe (the other unit bounds this pass)
+            const int pair0 = (tk * (GG / 4) + q4) * 2;
+            const float2 e01 = (pair0 % kScorePolyEvery == kScorePolyEvery - 1) ? exp2_poly2(x01) : make_float2(fast_exp2(x01.x), fast_exp2(x01.y));
+            const float2 e23 = ((pair0 + 1) % kScorePolyEvery == kScorePolyEvery - 1) ? exp2_poly2(x23) : make_float2(fast_exp2(x23.x), fast_exp2(x23.y));
+            e[q4 * 4 + 0] = e01.x;
+            e[q4 * 4 + 1] = e01.y;
             e[q4 * 4 + 2] = e23.x;
             e[q4 * 4 + 3] = e23.y;
           }
