@@ -219,71 +219,113 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       // Key tiles that every row of the warp sees in full (all but those on the mask's edge) take a path without the
       // per-element mask instructions.
       const bool full = __all_sync(0xffffffffu, lim >= kTcKeyTile && lo <= 0);
-      // ---- pass 1: row maximum of the raw logits (the scale is positive) ----
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-      auto pass1 = [&](auto masked_tag) {
-        constexpr bool MASKED = decltype(masked_tag)::value;
+      // The two-pass form: row maximum first, then the exponentials relative to the (possibly raised) reference.
+      auto two_pass = [&]() {
+        // ---- pass 1: row maximum of the raw logits (the scale is positive) ----
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        auto pass1 = [&](auto masked_tag) {
+          constexpr bool MASKED = decltype(masked_tag)::value;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t su[32];
-          tmem_ld32(s_base + c * 32, su);
-          tmem_ld_wait();
+          for (int c = 0; c < 4; ++c) {
+            uint32_t su[32];
+            tmem_ld32(s_base + c * 32, su);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            const float v0 = (!MASKED || (c * 32 + j < lim && c * 32 + j >= lo)) ? __uint_as_float(su[j]) : -INFINITY;
-            const float v1 = (!MASKED || (c * 32 + j + 1 < lim && c * 32 + j + 1 >= lo)) ? __uint_as_float(su[j + 1]) : -INFINITY;
-            mx4[(j >> 1) & 3] = fmax3(mx4[(j >> 1) & 3], v0, v1);
+            for (int j = 0; j < 32; j += 2) {
+              const float v0 = (!MASKED || (c * 32 + j < lim && c * 32 + j >= lo)) ? __uint_as_float(su[j]) : -INFINITY;
+              const float v1 = (!MASKED || (c * 32 + j + 1 < lim && c * 32 + j + 1 >= lo)) ? __uint_as_float(su[j + 1]) : -INFINITY;
+              mx4[(j >> 1) & 3] = fmax3(mx4[(j >> 1) & 3], v0, v1);
+            }
           }
+        };
+        if (full) pass1(std::false_type{}); else pass1(std::true_type{});
+        const float mt = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale2;
+        const bool need = mt > m_ref + 8.f;
+        float factor = 1.f;
+        if (need) {
+          factor = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - mt);
+          m_ref = mt;
+          l *= factor;
         }
-      };
-      if (full) pass1(std::false_type{}); else pass1(std::true_type{});
-      const float mt = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale2;
-      const bool need = mt > m_ref + 8.f;
-      float factor = 1.f;
-      if (need) {
-        factor = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - mt);
-        m_ref = mt;
-        l *= factor;
-      }
-      if (i > 0 && __any_sync(0xffffffffu, need)) {
-        mbar_wait(pv_done + g, (i - 1) & 1, p.st);  // P V of the previous key tile is complete: O is stable
-        tc_fence_after_sync();
+        if (i > 0 && __any_sync(0xffffffffu, need)) {
+          mbar_wait(pv_done + g, (i - 1) & 1, p.st);  // P V of the previous key tile is complete: O is stable
+          tc_fence_after_sync();
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(o_base + c * 32, r);
-          tmem_ld_wait();
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(o_base + c * 32, r);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            const float2 y = fmul2(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), make_float2(factor, factor));
-            r[j] = __float_as_uint(y.x);
-            r[j + 1] = __float_as_uint(y.y);
+            for (int j = 0; j < 32; j += 2) {
+              const float2 y = fmul2(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), make_float2(factor, factor));
+              r[j] = __float_as_uint(y.x);
+              r[j + 1] = __float_as_uint(y.y);
+            }
+            tmem_st32(o_base + c * 32, r);
           }
-          tmem_st32(o_base + c * 32, r);
+          tmem_st_wait();
         }
+        // ---- pass 2: P = exp2(S*scale - m_ref) as 16-bit pairs over the logits: the 32 columns of chunk c become the 16
+        // packed columns [16c, 16c+16), which lie inside chunk c/2 -- already consumed when chunk c is written ----
+        const float nm = (m_ref == -INFINITY) ? 0.f : -m_ref;
+        float2 ls2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+        auto pass2 = [&](auto masked_tag) {
+          constexpr bool MASKED = decltype(masked_tag)::value;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t su[32];
+            tmem_ld32(s_base + c * 32, su);
+            tmem_ld_wait();
+            uint32_t pk[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float2 x = ffma2(make_float2(__uint_as_float(su[2 * j]), __uint_as_float(su[2 * j + 1])), make_float2(p.scale2, p.scale2),
+                                     make_float2(nm, nm));
+              float p0, p1;
+              if (MASKED) {
+                p0 = masked_exp2(c * 32 + 2 * j < lim && c * 32 + 2 * j >= lo, x.x);
+                p1 = masked_exp2(c * 32 + 2 * j + 1 < lim && c * 32 + 2 * j + 1 >= lo, x.y);
+              } else if (j % kPolyEvery == kPolyEvery - 1) {  // a share of the exponentials runs on the FMA pipe
+                const float2 e = exp2_poly2(x);
+                p0 = e.x;
+                p1 = e.y;
+              } else {
+                p0 = fast_exp2(x.x);
+                p1 = fast_exp2(x.y);
+              }
+              ls2[j & 1] = fadd2(ls2[j & 1], make_float2(p0, p1));
+              pk[j] = DT<T>::pack(p0, p1);
+            }
+            tmem_st16(s_base + c * 16, pk);
+          }
+        };
+        if (full) pass2(std::false_type{}); else pass2(std::true_type{});
         tmem_st_wait();
-      }
-      // ---- pass 2: P = exp2(S*scale - m_ref) as 16-bit pairs over the logits: the 32 columns of chunk c become the 16
-      // packed columns [16c, 16c+16), which lie inside chunk c/2 -- already consumed when chunk c is written ----
-      const float nm = (m_ref == -INFINITY) ? 0.f : -m_ref;
-      float2 ls2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-      auto pass2 = [&](auto masked_tag) {
-        constexpr bool MASKED = decltype(masked_tag)::value;
+        l += (ls2[0].x + ls2[0].y) + (ls2[1].x + ls2[1].y);
+      };
+      // Full tiles of rows that already have a reference maximum are tried in ONE pass over the logits: exponentials
+      // relative to the current reference, with the maximum of the exponents tracked on the side.  If no row of the
+      // warp outgrew its reference by more than 2^8 -- the same test the two-pass form makes -- the packed P is stored
+      // and the pass for the maximum (four more TMEM loads) was saved; otherwise nothing has been written yet, the
+      // logits are intact, and the tile is redone in two passes.  Both routes give the same P and the same sums.
+      bool done = false;
+      if (full && __all_sync(0xffffffffu, m_ref != -INFINITY)) {
+        const float nm = -m_ref;
+        uint32_t pk[64];
+        float2 ls2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t su[32];
           tmem_ld32(s_base + c * 32, su);
           tmem_ld_wait();
-          uint32_t pk[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const float2 x = ffma2(make_float2(__uint_as_float(su[2 * j]), __uint_as_float(su[2 * j + 1])), make_float2(p.scale2, p.scale2),
                                    make_float2(nm, nm));
+            mx4[j & 3] = fmax3(mx4[j & 3], x.x, x.y);
             float p0, p1;
-            if (MASKED) {
-              p0 = masked_exp2(c * 32 + 2 * j < lim && c * 32 + 2 * j >= lo, x.x);
-              p1 = masked_exp2(c * 32 + 2 * j + 1 < lim && c * 32 + 2 * j + 1 >= lo, x.y);
-            } else if (j % kPolyEvery == kPolyEvery - 1) {  // a share of the exponentials runs on the FMA pipe
+            if (j % kPolyEvery == kPolyEvery - 1) {
               const float2 e = exp2_poly2(x);
               p0 = e.x;
               p1 = e.y;
@@ -292,14 +334,24 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
               p1 = fast_exp2(x.y);
             }
             ls2[j & 1] = fadd2(ls2[j & 1], make_float2(p0, p1));
-            pk[j] = DT<T>::pack(p0, p1);
+            pk[c * 16 + j] = DT<T>::pack(p0, p1);
           }
-          tmem_st16(s_base + c * 16, pk);
         }
-      };
-      if (full) pass2(std::false_type{}); else pass2(std::true_type{});
-      tmem_st_wait();
-      l += (ls2[0].x + ls2[0].y) + (ls2[1].x + ls2[1].y);
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        if (!__any_sync(0xffffffffu, mx > 8.f)) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t pc[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) pc[j] = pk[c * 16 + j];
+            tmem_st16(s_base + c * 16, pc);
+          }
+          tmem_st_wait();
+          l += (ls2[0].x + ls2[0].y) + (ls2[1].x + ls2[1].y);
+          done = true;
+        }
+      }
+      if (!done) two_pass();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full + g);
