@@ -13,7 +13,9 @@
 //                registers; dS phase (after dP): dS = P (dP - delta) scale -> TMEM.  They also compute
 //                delta = sum(O * dO) of their row up front and publish (lse, delta) for the dK/dV pass; at the end
 //                they store dQ
-//   warp 8     : TMA producer;   warp 9 : TMEM allocation and MMA issue (one thread)
+//                through shared memory and one TMA store per panel (row by row in the last CTA of a sequence)
+//   warp 8     : TMA producer (Q and the first K tile first, so that the first S product starts before dO, V and O have
+//                arrived);   warp 9 : TMEM allocation and MMA issue (one thread)
 #include "attn_bwd.h"
 #include "attn_tile.cuh"
 #include "dispatch.h"
@@ -30,7 +32,8 @@ constexpr int kDqVStages = 2;
 template <typename T, int D>
 __global__ void __launch_bounds__(320, 1)
 dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
-                   const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, DenseBwdParams p) {
+                   const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                   const __grid_constant__ CUtensorMap tmDQ, DenseBwdParams p) {
   constexpr int KT = 128;
   constexpr int PANELS = D / 64;
   constexpr int PANEL_BYTES = 128 * 128;
@@ -54,7 +57,8 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* all_done = ds_full + 1;
   uint64_t* o_full = all_done + 1;   // the O rows, staged in the last K stage for the delta computation
   uint64_t* o_done = o_full + 1;     // ... and read by all softmax warps
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
+  uint64_t* q_full = o_done + 1;     // the Q rows alone (the first S product needs only them and the first K tile)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (smem_u32(smem) & 1023u) {  // the swizzled operand tiles need a 1024-byte aligned base
@@ -94,6 +98,7 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(all_done, 1);
     mbar_init(o_full, 1);
     mbar_init(o_done, 8);
+    mbar_init(q_full, 1);
     fence_barrier_init();
   }
   if (warp == 9) {
@@ -108,18 +113,13 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == 8) {
     // ===================== TMA producer =====================
     if (lane == 0 && ntiles > 0) {
-      mbar_expect_tx(qdo_full, 2 * ROW_BYTES);
+      // Order of arrival: Q and the first K tile (the first S product can start), then dO and the first V tile (dP), then O
+      // (delta), then the remaining key tiles.
+      uint8_t* o_sm = k_sm + (kDqKStages - 1) * ROW_BYTES;  // the O rows borrow the last K stage, which the ring needs only
+                                                            // for its third tile
+      mbar_expect_tx(q_full, ROW_BYTES);
 #pragma unroll
-      for (int pn = 0; pn < PANELS; ++pn) {
-        tma_load_3d(q_sm + pn * PANEL_BYTES, &tmQ, qdo_full, pn * 64, h * p.G, qs + q0);
-        tma_load_3d(do_sm + pn * PANEL_BYTES, &tmDO, qdo_full, pn * 64, h * p.G, qs + q0);
-      }
-      // delta = rowsum(O * dO) is computed from SMEM: the O rows borrow the last K stage, which the ring needs only
-      // for its third tile
-      uint8_t* o_sm = k_sm + (kDqKStages - 1) * ROW_BYTES;
-      mbar_expect_tx(o_full, ROW_BYTES);
-#pragma unroll
-      for (int pn = 0; pn < PANELS; ++pn) tma_load_3d(o_sm + pn * PANEL_BYTES, &tmO, o_full, pn * 64, h * p.G, qs + q0);
+      for (int pn = 0; pn < PANELS; ++pn) tma_load_3d(q_sm + pn * PANEL_BYTES, &tmQ, q_full, pn * 64, h * p.G, qs + q0);
       for (int i = 0; i < ntiles; ++i) {
         const int sk = i % kDqKStages, sv = i % kDqVStages;
         if (i >= kDqKStages) mbar_wait(k_empty + sk, ((i / kDqKStages) - 1) & 1, p.st);
@@ -128,11 +128,21 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
         for (int pn = 0; pn < PANELS; ++pn)
           tma_load_3d(k_sm + sk * ROW_BYTES + pn * PANEL_BYTES, &tmK, k_full + sk, pn * 64, h, ksq + (kt0 + i) * KT);
+        if (i == 0) {
+          mbar_expect_tx(qdo_full, ROW_BYTES);
+#pragma unroll
+          for (int pn = 0; pn < PANELS; ++pn) tma_load_3d(do_sm + pn * PANEL_BYTES, &tmDO, qdo_full, pn * 64, h * p.G, qs + q0);
+        }
         if (i >= kDqVStages) mbar_wait(v_empty + sv, ((i / kDqVStages) - 1) & 1, p.st);
         mbar_expect_tx(v_full + sv, ROW_BYTES);
 #pragma unroll
         for (int pn = 0; pn < PANELS; ++pn)
           tma_load_3d(v_sm + sv * ROW_BYTES + pn * PANEL_BYTES, &tmV, v_full + sv, pn * 64, h, ksq + (kt0 + i) * KT);
+        if (i == 0) {
+          mbar_expect_tx(o_full, ROW_BYTES);
+#pragma unroll
+          for (int pn = 0; pn < PANELS; ++pn) tma_load_3d(o_sm + pn * PANEL_BYTES, &tmO, o_full, pn * 64, h * p.G, qs + q0);
+        }
       }
     }
   } else if (warp == 9) {
@@ -142,7 +152,7 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const uint32_t idesc_s = umma_idesc<T>(128, KT, false, false);
       const uint32_t idesc_q = umma_idesc<T>(128, D, false, true);
       const uint32_t q_addr = smem_u32(q_sm), do_addr = smem_u32(do_sm), k_base = smem_u32(k_sm), v_base = smem_u32(v_sm);
-      mbar_wait(qdo_full, 0, p.st);
+      mbar_wait(q_full, 0, p.st);
       // S(i) may start once the softmax threads have read S(i-1); dP(i) once dQ(i-1) has been issued (it overwrites
       // dS(i-1); the pipe executes in issue order); dQ(i) needs dS(i).
       int ns = 0, np = 0, nq = 0;
@@ -172,7 +182,8 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           ++nq;
           progressed = true;
         }
-        if (np < ntiles && np == nq && np < ns && mbar_test(v_full + (np % kDqVStages), (np / kDqVStages) & 1)) {
+        if (np < ntiles && np == nq && np < ns && mbar_test(v_full + (np % kDqVStages), (np / kDqVStages) & 1) &&
+            (np > 0 || mbar_test(qdo_full, 0))) {  // the first dP also needs the dO rows
           tc_fence_after_sync();
           const int sv = np % kDqVStages;
           if (elect_one()) {
@@ -297,6 +308,10 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_wait(all_done, 0, p.st);
       tc_fence_after_sync();
     }
+    // A CTA whose rows all belong to its sequence stages the tile in shared memory (the first K stage, free by now, in the
+    // swizzled panel layout the loads use) and writes it with one TMA store per panel: 16-byte stores of one row per lane
+    // cost several thousand clocks of the store path per CTA.  Other CTAs (the last of a sequence) store row by row.
+    const bool staged = ntiles > 0 && q0 + QT <= Lq;
     T* dqrow = static_cast<T*>(p.dq) + (long long)(qs + tpos) * p.dq_sn + (long long)head * p.dq_sh + half * (D / 2);
 #pragma unroll
     for (int c = 0; c < D / 64; ++c) {
@@ -308,7 +323,19 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
         for (int j = 0; j < 32; ++j) r[j] = 0u;
       }
-      if (valid) {
+      if (staged) {
+        const uint32_t stage = smem_u32(k_sm);
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int ci = (half * (D / 2) + c * 32) / 8 + q4;  // 16-byte chunk of the row
+          const uint32_t off = (ci >> 3) * PANEL_BYTES + row * 128 + (((ci & 7) ^ (row & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(stage + off),
+                       "r"(DT<T>::pack(__uint_as_float(r[q4 * 8 + 0]), __uint_as_float(r[q4 * 8 + 1]))),
+                       "r"(DT<T>::pack(__uint_as_float(r[q4 * 8 + 2]), __uint_as_float(r[q4 * 8 + 3]))),
+                       "r"(DT<T>::pack(__uint_as_float(r[q4 * 8 + 4]), __uint_as_float(r[q4 * 8 + 5]))),
+                       "r"(DT<T>::pack(__uint_as_float(r[q4 * 8 + 6]), __uint_as_float(r[q4 * 8 + 7]))) : "memory");
+        }
+      } else if (valid) {
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           uint4 out;
@@ -318,6 +345,16 @@ dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           out.w = DT<T>::pack(__uint_as_float(r[q4 * 8 + 6]), __uint_as_float(r[q4 * 8 + 7]));
           *reinterpret_cast<uint4*>(dqrow + c * 32 + q4 * 8) = out;
         }
+      }
+    }
+    if (staged) {
+      fence_proxy_async();  // the TMA engine reads the tile through the async proxy
+      asm volatile("bar.sync 1, 256;\n" ::: "memory");
+      if (threadIdx.x == 0) {
+#pragma unroll
+        for (int pn = 0; pn < PANELS; ++pn) tma_store_3d(&tmDQ, k_sm + pn * PANEL_BYTES, pn * 64, h * p.G, qs + q0);
+        tma_store_commit();
+        tma_store_wait_read();
       }
     }
   }
@@ -341,12 +378,15 @@ static int launch_dense_dq_tc(const void* k, const void* v, long long k_sn, long
   if (rc) return rc;
   rc = make_tmap_3d(&tmV, DT<T>::kTmapType, v, D, p.Hkv, total_k, v_sh, v_sn, 64, 1, 128);
   if (rc) return rc;
+  CUtensorMap tmDQ;
+  rc = make_tmap_3d(&tmDQ, DT<T>::kTmapType, p.dq, D, p.Hq, total_q, p.dq_sh, p.dq_sn, 64, p.G, QT);
+  if (rc) return rc;
   const size_t smem = (size_t)(2 + kDqKStages + kDqVStages) * (128 * D * 2) + 256 * sizeof(float) + 24 * sizeof(uint64_t) + 16;
   auto kern = dense_dq_tc_kernel<T, D>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_rc(e);
   dim3 grid((max_seqlen_q + QT - 1) / QT, p.B, p.Hkv);
-  { LaunchScope ls_("dense_dq_tc", stream); kern<<<grid, 320, smem, stream>>>(tmQ, tmDO, tmO, tmK, tmV, p); }
+  { LaunchScope ls_("dense_dq_tc", stream); kern<<<grid, 320, smem, stream>>>(tmQ, tmDO, tmO, tmK, tmV, tmDQ, p); }
   return cuda_rc(cudaGetLastError());
 }
 
