@@ -431,11 +431,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=None, help="override the sequence length (parity/debug only)")
+    ap.add_argument("--topk", type=int, default=None, help="override the number of selected blocks (size sweep only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode-operator micro-benchmark")
     args = ap.parse_args()
     if args.tokens:
         WORKLOAD["tokens"] = args.tokens
+    if args.topk:
+        WORKLOAD["topk"] = args.topk
 
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
