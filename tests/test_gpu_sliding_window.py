@@ -50,6 +50,19 @@ def test_sliding_window_forward_backward(ops, Hq, Hkv, seqlens, window):
     assert status_ok()
 
 
+@pytest.mark.parametrize("seed", range(8))
+def test_sliding_window_random_configurations(ops, seed):
+    """Seeded random group sizes, ragged batches (sequences that end inside a row tile, so that both the staged and the
+    row-by-row output paths of the dQ pass run) and windows."""
+    import random
+    rnd = random.Random(100 + seed)
+    Hkv = rnd.choice([1, 2, 4])
+    G = rnd.choice([1, 2, 4, 8, 16])
+    seqlens = [rnd.choice([rnd.randint(1, 40), rnd.randint(60, 500), rnd.randint(500, 1200)]) for _ in range(rnd.choice([1, 2, 4]))]
+    window = rnd.choice([0, 1, rnd.randint(2, 127), 128, rnd.randint(129, 600), 5000])
+    test_sliding_window_forward_backward(ops, Hkv * G, Hkv, seqlens, window)
+
+
 def test_window_covers_everything_equals_causal(ops):
     """With a window at least as long as the sequences the result is the plain causal attention of flash_attention_varlen."""
     x = chain_inputs(12, [400, 77], 16, 2, 128, 32)
