@@ -1,0 +1,69 @@
+"""The operators composed as the reference's layer composes them (module/native_sparse_attention.py:146-236): compression of
+the un-rotated keys/values, rotary embedding of q / compressed k / k, compressed attention with block selection, selected-
+block attention, sliding-window attention, the gated sum -- forward and backward through ALL of them at once under autograd,
+against the same composition of the oracle's functions in fp32 (selection taken from the GPU so that a tie cannot move a
+block).  Each operator has its own parity test; this one checks that gradients flow through the whole chain (rope backward
+into compression backward, three branches accumulating into q, k and v)."""
+import math
+
+import pytest
+import torch
+
+from oracle import nsa_oracle as O
+from tests.helpers import chain_inputs
+from tests.test_gpu_backward import close, status_ok
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("Hq,Hkv,seqlens,topk,window", [(16, 2, [300, 129, 40], 4, 64), (32, 2, [900], 8, 512)])
+def test_layer_forward_backward(Hq, Hkv, seqlens, topk, window):
+    import native_sparse_attention_triton_b200 as pkg
+    ops = pkg.ops
+    d, ks, st, bs = 128, 32, 16, 64
+    x = chain_inputs(21, seqlens, Hq, Hkv, d, ks)
+    g = torch.Generator().manual_seed(5)
+    N = sum(seqlens)
+    gate = torch.rand(N, Hq, 3, generator=g).bfloat16().float()
+    dy = torch.randn(N, Hq, d, generator=g).bfloat16().float()
+    inv_freq = 1.0 / (500000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    names = ("q", "k", "v", "wk", "wv", "pe")
+    cu = x["cu"]
+
+    # ---- this library, bf16 on the GPU ----
+    t = {n: x[n].bfloat16().cuda().requires_grad_(True) for n in names}
+    gate_g = gate.bfloat16().cuda().requires_grad_(True)
+    cu_g, f_g = cu.cuda(), inv_freq.cuda()
+    ck, cu_k = ops.linear_compress(t["k"], t["wk"], cu_g, ks, st, t["pe"])
+    cv, _ = ops.linear_compress(t["v"], t["wv"], cu_g, ks, st, None)
+    q_r = ops.rope(t["q"], f_g, cu_g)
+    ck_r = ops.rope(ck, f_g, cu_k, 0, st)
+    k_r = ops.rope(t["k"], f_g, cu_g)
+    o_cmp, idx = ops.compressed_attention(q_r, ck_r, cv, ks, st, bs, topk, cu_g, cu_k, max(seqlens), int((cu_k[1:] - cu_k[:-1]).max()),
+                                          None, 1, 2)
+    o_sel = ops.topk_sparse_attention(q_r, k_r, t["v"], idx, bs, cu_g)
+    o_win = ops.sliding_window_attention(q_r, k_r, t["v"], cu_g, max(seqlens), window)
+    y = ops.gate_combine(gate_g, o_cmp, o_sel, o_win)
+    y.backward(dy.bfloat16().cuda())
+
+    # ---- the oracle, fp32 on the CPU, with the GPU's selection ----
+    r = {n: x[n].clone().requires_grad_(True) for n in names}
+    gate_r = gate.clone().requires_grad_(True)
+    ck2, cu_k2 = O.linear_compress(r["k"], r["wk"], cu, ks, st, r["pe"])
+    cv2, _ = O.linear_compress(r["v"], r["wv"], cu, ks, st, None)
+    q2 = O.rope(r["q"], inv_freq, cu)
+    ck2r = O.rope(ck2, inv_freq, cu_k2, 0, st)
+    k2 = O.rope(r["k"], inv_freq, cu)
+    o_cmp2 = O.compressed_attention(q2, ck2r, cv2, ks, st, bs, topk, cu, cu_k2, init_blocks=1, local_blocks=2)[0]
+    o_sel2 = O.topk_sparse_attention(q2, k2, r["v"], idx.cpu(), bs, cu)
+    o_win2 = O.sliding_window_attention(q2, k2, r["v"], cu, window)
+    y2 = O.gate_combine(gate_r, o_cmp2, o_sel2, o_win2)
+    y2.backward(dy)
+
+    err = (y.detach().float().cpu() - y2.detach()).abs()
+    # three branch outputs, each within the operator tolerance (2e-2 / 2e-3), computed from 16-bit rotated inputs and summed
+    assert float((err / y2.detach().abs().clamp(min=1.0)).max()) <= 4e-2 and float(err.mean()) <= 3e-3
+    for n in names:
+        close(t[n].grad, r[n].grad, "d" + n)
+    close(gate_g.grad, gate_r.grad, "dgate")
+    assert status_ok()
