@@ -295,6 +295,13 @@ int nsa_rope_decode(const void* x, void* y, const float* inv_freq, const int* le
                     int stride, float attention_scaling, int inverse, long long x_stride_n, long long x_stride_h,
                     long long y_stride_n, long long y_stride_h, int dtype, void* stream);
 
+/* The three rotations of one decode step in one launch: query [batch, num_q_heads, d] and key [batch, num_kv_heads, d] at
+ * position lengths_qk[b], compressed key [batch, num_kv_heads, d] at lengths_ck[b] * stride_ck (infer/nsa_inference.py:94-103
+ * with step > 0).  strides[12] = {x_n, x_h, y_n, y_h} for query, key, compressed key.  Otherwise as nsa_rope_decode. */
+int nsa_rope_decode3(const void* q, void* yq, const void* k, void* yk, const void* ck, void* yck, const float* inv_freq,
+                     const int* lengths_qk, const int* lengths_ck, int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                     int stride_ck, float attention_scaling, const long long* strides, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

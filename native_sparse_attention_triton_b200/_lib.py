@@ -38,6 +38,7 @@ _SIGNATURES = {
     "nsa_gate_combine_bwd": [_P] * 9 + [_I, _I, _I, _P, _I, _P],
     "nsa_rope": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _L, _L, _L, _L, _I, _P],
     "nsa_rope_decode": [_P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _L, _L, _L, _L, _I, _P],
+    "nsa_rope_decode3": [_P] * 9 + [_I, _I, _I, _I, _I, _F, _P, _I, _P],
     "nsa_kv_cache_fill": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "nsa_kv_cache_stage_decode": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "nsa_kv_cache_append_decode": [_P] * 13 + [_I] * 7 + [_P, _P],

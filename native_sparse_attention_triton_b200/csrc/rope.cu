@@ -34,13 +34,13 @@ __device__ __forceinline__ uint4 ld16(const void* p) {
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__(256) rope_kernel(RopeParams p) {
+__device__ __forceinline__ void rope_rows(const RopeParams& p, int first_block, int num_blocks) {
   constexpr int HALF = D / 2;
   constexpr int TOK = 256 / HALF;  // tokens whose tables one CTA holds at a time
   constexpr int CH = HALF / 8;     // 16-byte chunks per half row
   __shared__ float cs[TOK][HALF], sn[TOK][HALF];
   const int tid = threadIdx.x;
-  for (int tok0 = blockIdx.x * TOK; tok0 < p.N; tok0 += gridDim.x * TOK) {
+  for (int tok0 = first_block * TOK; tok0 < p.N; tok0 += num_blocks * TOK) {
     {
       const int tl = tid / HALF, j = tid % HALF, n = tok0 + tl;
       if (n < p.N) {
@@ -85,6 +85,28 @@ __global__ void __launch_bounds__(256) rope_kernel(RopeParams p) {
     }
     __syncthreads();
   }
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(256) rope_kernel(RopeParams p) {
+  rope_rows<T, D>(p, blockIdx.x, gridDim.x);
+}
+
+// The three rotations of a decode step (query, key, compressed key) in one launch: blockIdx.y picks the tensor.
+struct Rope3Params {
+  RopeParams seg[3];
+};
+template <typename T, int D>
+__global__ void __launch_bounds__(256) rope3_kernel(Rope3Params p) {
+  rope_rows<T, D>(p.seg[blockIdx.y], blockIdx.x, gridDim.x);
+}
+
+template <typename T, int D>
+static int launch_rope3(Rope3Params p, cudaStream_t stream) {
+  constexpr int TOK = 256 / (D / 2);
+  LaunchScope ls_("rope3", stream);
+  rope3_kernel<T, D><<<dim3((p.seg[0].N + TOK - 1) / TOK, 3), 256, 0, stream>>>(p);
+  return cuda_rc(cudaGetLastError());
 }
 
 template <typename T, int D>
@@ -133,4 +155,27 @@ extern "C" int nsa_rope_decode(const void* x, void* y, const float* inv_freq, co
   p.N = batch; p.B = batch; p.H = num_heads; p.step = -1; p.stride = stride; p.inverse = inverse ? 1 : 0;
   p.scaling = attention_scaling;
   return NSA_DISPATCH_T_D(dtype, head_dim, launch_rope, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nsa_rope_decode3(const void* q, void* yq, const void* k, void* yk, const void* ck, void* yck,
+                                const float* inv_freq, const int* lengths_qk, const int* lengths_ck, int batch,
+                                int num_q_heads, int num_kv_heads, int head_dim, int stride_ck, float attention_scaling,
+                                const long long* strides, int dtype, void* stream) {
+  using namespace nsa;
+  if (!inv_freq || !lengths_qk || !lengths_ck || !strides || batch <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || stride_ck <= 0)
+    return kInvalid;
+  const void* x[3] = {q, k, ck};
+  void* y[3] = {yq, yk, yck};
+  Rope3Params p;
+  for (int i = 0; i < 3; ++i) {
+    if (!x[i] || !y[i] || !aligned16(x[i]) || !aligned16(y[i])) return kInvalid;
+    const long long* st = strides + 4 * i;
+    if ((st[0] | st[1] | st[2] | st[3]) % 8) return kInvalid;
+    RopeParams& r = p.seg[i];
+    r.x = x[i]; r.y = y[i]; r.inv_freq = inv_freq; r.cu = i == 2 ? lengths_ck : lengths_qk;
+    r.x_sn = st[0]; r.x_sh = st[1]; r.y_sn = st[2]; r.y_sh = st[3];
+    r.N = batch; r.B = batch; r.H = i == 0 ? num_q_heads : num_kv_heads; r.step = -1; r.stride = i == 2 ? stride_ck : 1;
+    r.inverse = 0; r.scaling = attention_scaling;
+  }
+  return NSA_DISPATCH_T_D(dtype, head_dim, launch_rope3, p, static_cast<cudaStream_t>(stream));
 }

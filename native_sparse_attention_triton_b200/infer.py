@@ -44,6 +44,25 @@ class RotaryEmbedding:
         return y
 
 
+    def decode_at3(self, query, key, compress_key, lengths_qk, lengths_ck, stride_ck: int):
+        """The three rotations of a decode step in one launch: query and key at lengths_qk[b], the compressed key at
+        lengths_ck[b] * stride_ck."""
+        xs = [inner_contiguous(t) for t in (query, key, compress_key)]
+        ys = [torch.empty(t.shape, dtype=t.dtype, device=t.device) for t in xs]
+        batch, num_q_heads, head_dim = xs[0].shape
+        num_kv_heads = xs[1].shape[1]
+        assert xs[1].shape == xs[2].shape == (batch, num_kv_heads, head_dim)
+        assert lengths_qk.dtype == torch.int32 and lengths_ck.dtype == torch.int32
+        strides = _lib.strides_array(*[s for x, y in zip(xs, ys) for s in (x.stride(0), x.stride(1), y.stride(0), y.stride(1))])
+        torch.cuda.set_device(xs[0].device)
+        rc = _lib.lib().nsa_rope_decode3(ptr(xs[0]), ptr(ys[0]), ptr(xs[1]), ptr(ys[1]), ptr(xs[2]), ptr(ys[2]), ptr(self.inv_freq),
+                                         ptr(lengths_qk), ptr(lengths_ck), batch, num_q_heads, num_kv_heads, head_dim,
+                                         int(stride_ck), self.attention_scaling, strides, dtype_code(xs[0]),
+                                         stream_ptr(xs[0].device))
+        _lib.check(rc, "nsa_rope_decode3")
+        return ys
+
+
 def _compress_staged(cache: NSACache, batch: int, which: int, func: Callable, weight, pe):
     """One compressed row per sequence from the staging buffers [batch * kernel_size, heads, d] (the reference runs its
     compress function over them with an arange cu_seqlens, infer/inference_func.py:56-87).  The library's own compress
@@ -107,11 +126,10 @@ def nsa_infer(cu_seqlens: torch.Tensor, step: int, query: torch.Tensor, key: tor
     cache.prepare_compress(cu_seqlens, step, key, value)
     compress_key = _compress_staged(cache, batch, 0, compress_func[0], compress_weight[0], intra_block_pe)
     compress_value = _compress_staged(cache, batch, 1, compress_func[1], compress_weight[1], None)
-    if hasattr(rope, "decode_at"):
+    if hasattr(rope, "decode_at3"):
         # the new token's index is the number of tokens cached so far; the compressed token's, the compressed count
-        query = rope.decode_at(query, cache.sparse_kv_len, 1)
-        key = rope.decode_at(key, cache.sparse_kv_len, 1)
-        compress_key = rope.decode_at(compress_key, cache.compress_kv_len, kernel_stride)
+        query, key, compress_key = rope.decode_at3(query, key, compress_key, cache.sparse_kv_len, cache.compress_kv_len,
+                                                    kernel_stride)
     else:
         compress_cu = torch.zeros(batch + 1, dtype=torch.int32, device=key.device)
         compress_cu[1:] = torch.cumsum(cache.compress_kv_len[:batch], 0)

@@ -92,3 +92,23 @@ def test_rope_in_place_and_argument_checks(ops):
         ops.rope(x.float(), inv_freq, cu)
     with pytest.raises(AssertionError):
         ops.rope(x, inv_freq[:32], cu)
+
+
+def test_three_decode_rotations_in_one_launch_equal_three_launches(ops):
+    from native_sparse_attention_triton_b200.infer import RotaryEmbedding
+    g = torch.Generator().manual_seed(8)
+    B, Hq, Hkv, d = 5, 16, 2, 128
+    rope = RotaryEmbedding(inv_freq_for(d).cuda(), 0.9)
+    q = torch.randn(B, Hq, d, generator=g).bfloat16().cuda()
+    k = torch.randn(B, Hkv, d, generator=g).bfloat16().cuda()
+    ck = torch.randn(B, Hkv, d, generator=g).bfloat16().cuda()
+    lens = torch.tensor([0, 5, 8191, 77, 1000], dtype=torch.int32).cuda()
+    clens = torch.tensor([0, 0, 510, 3, 61], dtype=torch.int32).cuda()
+    yq, yk, yck = rope.decode_at3(q, k, ck, lens, clens, 16)
+    assert torch.equal(yq, rope.decode_at(q, lens, 1))
+    assert torch.equal(yk, rope.decode_at(k, lens, 1))
+    assert torch.equal(yck, rope.decode_at(ck, clens, 16))
+    # and a row at a device-side length equals the prefill rotation of the token at that index
+    cu = torch.tensor([0, 78], dtype=torch.int32).cuda()
+    full = ops.rope(q[3:4].expand(78, Hq, d).contiguous(), rope.inv_freq, cu, 0, 1, 0.9)
+    assert torch.equal(full[77], yq[3])
