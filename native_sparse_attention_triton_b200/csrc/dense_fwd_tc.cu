@@ -3,7 +3,8 @@
 //
 // CTA = two row tiles A and B of 128 rows each; a row tile is (128/G consecutive query tokens) x (G query heads of one
 // KV head); B holds the tokens right after A's.  Key tiles of 128 go through SMEM rings shared by both row tiles.
-//   warp 8      : TMA producer (Q of both tiles once, then K tiles through a ring of 3 and V tiles through a ring of 2)
+//   warp 8      : TMA producer (Q of tile A and the first K tile first, so that the first product starts early, then Q of
+//                 tile B, K tiles through a ring of 3 and V tiles through a ring of 2)
 //   warp 9      : allocates TMEM; issues, per key tile and row tile, S = Q K^T (SMEM x SMEM -> TMEM) and O += P V
 //                 (P read from TMEM, V from SMEM MN-major), alternating between the two row tiles: while the softmax
 //                 threads of one tile work, the tensor pipe runs the other tile's products
@@ -11,7 +12,8 @@
 //                 finds the row maximum, a second pass reads them again, exponentiates and writes P as 16-bit pairs
 //                 back into tensor memory over the logits, where the P V instruction reads its A operand -- P never
 //                 touches shared memory.  A lazily updated reference maximum is kept: O and l are rescaled only when the
-//                 row maximum grows by more than 2^8.  At the end the threads normalise O and store it
+//                 row maximum grows by more than 2^8.  At the end the threads normalise O and store it (through the tile's Q
+//                 buffer and a TMA store when all of the tile's tokens belong to the sequence)
 //   warps 4..7  : the same for tile B
 // The tensor pipe executes one thread's MMAs in issue order, so S(i+1) of a row tile, issued after its P V(i), cannot
 // overwrite P(i) before it has been read.
@@ -57,7 +59,7 @@ constexpr int kTcVStages = 2;  // a V tile is free when both row tiles' P V are 
 template <typename T, int D>
 __global__ void __launch_bounds__(320, 1)
 dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                    const __grid_constant__ CUtensorMap tmV, DenseFwdTcParams p) {
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, DenseFwdTcParams p) {
   constexpr int PANELS = D / 64;
   constexpr int PANEL_BYTES = 128 * 128;            // 128 rows x 128 B
   constexpr int Q_BYTES = 128 * D * 2;              // one row tile
@@ -75,7 +77,8 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* s_full = v_empty + kTcVStages;   // [2] per row tile
   uint64_t* p_full = s_full + 2;             // [2]
   uint64_t* pv_done = p_full + 2;            // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+  uint64_t* qb_full = pv_done + 2;           // Q of row tile B (q_full covers tile A alone: the first product needs only it)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(qb_full + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (smem_u32(smem) & 1023u) {  // the swizzled operand tiles need a 1024-byte aligned base
@@ -96,6 +99,7 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(qb_full, 1);
     for (int s = 0; s < kTcKStages; ++s) {
       mbar_init(k_full + s, 1);
       mbar_init(k_empty + s, 1);
@@ -123,12 +127,10 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == 8) {
     // ===================== TMA producer =====================
     if (lane == 0 && ntiles > 0) {
-      mbar_expect_tx(q_full, 2 * Q_BYTES);
+      // Q of tile A and the first K tile arrive first (the first product can start), then Q of tile B
+      mbar_expect_tx(q_full, Q_BYTES);
 #pragma unroll
-      for (int g = 0; g < 2; ++g)
-#pragma unroll
-        for (int pn = 0; pn < PANELS; ++pn)
-          tma_load_3d(q_sm + g * Q_BYTES + pn * PANEL_BYTES, &tmQ, q_full, pn * 64, h * p.G, qs + q0 + g * QT);
+      for (int pn = 0; pn < PANELS; ++pn) tma_load_3d(q_sm + pn * PANEL_BYTES, &tmQ, q_full, pn * 64, h * p.G, qs + q0);
       // K runs one tile ahead of V: tile i's V is requested after tile i+1's K
       for (int i = 0; i <= ntiles; ++i) {
         if (i < ntiles) {
@@ -138,6 +140,12 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
           for (int pn = 0; pn < PANELS; ++pn)
             tma_load_3d(k_sm + s * KV_BYTES + pn * PANEL_BYTES, &tmK, k_full + s, pn * 64, h, ksq + (kt0 + i) * kTcKeyTile);
+        }
+        if (i == 0) {
+          mbar_expect_tx(qb_full, Q_BYTES);
+#pragma unroll
+          for (int pn = 0; pn < PANELS; ++pn)
+            tma_load_3d(q_sm + Q_BYTES + pn * PANEL_BYTES, &tmQ, qb_full, pn * 64, h * p.G, qs + q0 + QT);
         }
         if (i >= 1) {
           const int j = i - 1, s = j % kTcVStages;
@@ -182,6 +190,8 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_wait(k_full, 0, p.st);
       tc_fence_after_sync();
       issue_qk(0, 0);
+      mbar_wait(qb_full, 0, p.st);
+      tc_fence_after_sync();
       issue_qk(0, 1);
       for (int i = 0; i < ntiles; ++i) {
 #pragma unroll
@@ -363,6 +373,9 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     const float inv = l > 0.f ? 1.f / l : 0.f;
     if (valid) p.lse[(long long)(qs + tpos) * p.Hq + head] = l > 0.f ? m_ref + log2f(l) : -INFINITY;
+    // A row tile whose tokens all belong to the sequence leaves through shared memory (its own Q buffer, free since its
+    // last S product, in the swizzled panel layout) and one TMA store per panel; otherwise row by row.
+    const bool staged = ntiles > 0 && q0 + g * QT + QT <= Lq;
     T* orow = static_cast<T*>(p.o) + (long long)(qs + tpos) * p.o_sn + (long long)head * p.o_sh;
 #pragma unroll
     for (int c = 0; c < D / 32; ++c) {
@@ -374,7 +387,19 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
         for (int j = 0; j < 32; ++j) r[j] = 0u;
       }
-      if (valid) {
+      if (staged) {
+        const uint32_t stage = smem_u32(q_sm + g * Q_BYTES);
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int ci = c * 4 + q4;  // 16-byte chunk of the row
+          const uint32_t off = (ci >> 3) * PANEL_BYTES + row * 128 + (((ci & 7) ^ (row & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(stage + off),
+                       "r"(DT<T>::pack(__uint_as_float(r[q4 * 8 + 0]) * inv, __uint_as_float(r[q4 * 8 + 1]) * inv)),
+                       "r"(DT<T>::pack(__uint_as_float(r[q4 * 8 + 2]) * inv, __uint_as_float(r[q4 * 8 + 3]) * inv)),
+                       "r"(DT<T>::pack(__uint_as_float(r[q4 * 8 + 4]) * inv, __uint_as_float(r[q4 * 8 + 5]) * inv)),
+                       "r"(DT<T>::pack(__uint_as_float(r[q4 * 8 + 6]) * inv, __uint_as_float(r[q4 * 8 + 7]) * inv)) : "memory");
+        }
+      } else if (valid) {
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           uint4 out;
@@ -384,6 +409,16 @@ dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           out.w = DT<T>::pack(__uint_as_float(r[q4 * 8 + 6]) * inv, __uint_as_float(r[q4 * 8 + 7]) * inv);
           *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = out;
         }
+      }
+    }
+    if (staged) {
+      fence_proxy_async();  // the TMA engine reads the tile through the async proxy
+      asm volatile("bar.sync %0, 128;\n" ::"r"(1 + g) : "memory");
+      if ((warp & 3) == 0 && lane == 0) {
+#pragma unroll
+        for (int pn = 0; pn < PANELS; ++pn) tma_store_3d(&tmO, q_sm + g * Q_BYTES + pn * PANEL_BYTES, pn * 64, h * p.G, qs + q0 + g * QT);
+        tma_store_commit();
+        tma_store_wait_read();
       }
     }
   }
@@ -404,12 +439,15 @@ static int launch_dense_fwd_tc(const void* q, const void* k, const void* v, cons
   if (rc) return rc;
   rc = make_tmap_3d(&tmV, DT<T>::kTmapType, v, D, p.Hkv, Nk, S[5], S[4], 64, 1, kTcKeyTile);
   if (rc) return rc;
+  CUtensorMap tmO;
+  rc = make_tmap_3d(&tmO, DT<T>::kTmapType, p.o, D, p.Hq, Nq, p.o_sh, p.o_sn, 64, p.G, QT);
+  if (rc) return rc;
   const size_t smem = 2 * 128 * D * 2 + (kTcKStages + kTcVStages) * kTcKeyTile * D * 2 + 32 * sizeof(uint64_t);
   auto kern = dense_fwd_tc_kernel<T, D>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_rc(e);
   dim3 grid((max_seqlen_q + 2 * QT - 1) / (2 * QT), p.B, p.Hkv);
-  { LaunchScope ls_("dense_fwd_tc", stream); kern<<<grid, 320, smem, stream>>>(tmQ, tmK, tmV, p); }
+  { LaunchScope ls_("dense_fwd_tc", stream); kern<<<grid, 320, smem, stream>>>(tmQ, tmK, tmV, tmO, p); }
   return cuda_rc(cudaGetLastError());
 }
 
