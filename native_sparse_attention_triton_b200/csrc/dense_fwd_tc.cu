@@ -11,7 +11,8 @@
 //   warps 0..3  : softmax of tile A, one thread per row (TMEM lane): a first pass over the 128 logits of the key tile
 //                 finds the row maximum, a second pass reads them again, exponentiates and writes P as 16-bit pairs
 //                 back into tensor memory over the logits, where the P V instruction reads its A operand -- P never
-//                 touches shared memory.  A lazily updated reference maximum is kept: O and l are rescaled only when the
+//                 touches shared memory.  (Full tiles of rows that already have a reference maximum take a single pass,
+//                 see the loop.)  A lazily updated reference maximum is kept: O and l are rescaled only when the
 //                 row maximum grows by more than 2^8.  At the end the threads normalise O and store it (through the tile's Q
 //                 buffer and a TMA store when all of the tile's tokens belong to the sequence)
 //   warps 4..7  : the same for tile B
