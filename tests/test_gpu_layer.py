@@ -4,8 +4,6 @@ block attention, sliding-window attention, the gated sum -- forward and backward
 against the same composition of the oracle's functions in fp32 (selection taken from the GPU so that a tie cannot move a
 block).  Each operator has its own parity test; this one checks that gradients flow through the whole chain (rope backward
 into compression backward, three branches accumulating into q, k and v)."""
-import math
-
 import pytest
 import torch
 
