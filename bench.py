@@ -310,7 +310,6 @@ def decode_step_microbench(dev):
     attention branches + gated sum) at the shapes of the generation config (batch 4, 8192-token context, 32q/2kv heads,
     d=128, weighted-pool compression, top-8, window 512): launches per step, microseconds per step launched eagerly from
     Python and replayed from a CUDA graph."""
-    import math as _m
     from native_sparse_attention_triton_b200.infer import DecodeGraph, RotaryEmbedding, nsa_infer
     from native_sparse_attention_triton_b200.kv_cache import NSACache
     pkg = sys.modules["native_sparse_attention_triton_b200"]

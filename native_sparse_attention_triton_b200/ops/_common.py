@@ -1,6 +1,6 @@
 """Helpers shared by the operator wrappers: argument plumbing between torch tensors and the C ABI."""
 import math
-from typing import List, Tuple
+from typing import List
 
 import torch
 

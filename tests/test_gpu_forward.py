@@ -1,5 +1,4 @@
 """Forward parity of the CUDA operators (through the C ABI) against the CPU oracle and the golden fixtures."""
-import math
 
 import pytest
 import torch
