@@ -43,7 +43,6 @@ class RotaryEmbedding:
         _lib.check(rc, "nsa_rope_decode")
         return y
 
-
     def decode_at3(self, query, key, compress_key, lengths_qk, lengths_ck, stride_ck: int):
         """The three rotations of a decode step in one launch: query and key at lengths_qk[b], the compressed key at
         lengths_ck[b] * stride_ck."""
