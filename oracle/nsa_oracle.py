@@ -4,8 +4,8 @@ This module is the checker for the CUDA kernels of this repository.  It is never
 imported by the product package: only the tests, the smoke entry and the CPU
 baseline leg of the benchmark may use it.
 
-Every function restates, in plain fp32 torch on the CPU and with memory that is
-linear in the sequence length per query tile, what the reference project
+Every function restates, in plain fp32 torch (on the CPU; the tensors' device is
+followed, so a test may also evaluate it on a GPU in true fp32) what the reference project
 (XunhaoLai/native-sparse-attention-triton) computes.  The reference file and
 lines each function follows are cited in its docstring (paths are relative to
 the reference project root).  The restatement is pinned against the reference's
@@ -36,7 +36,7 @@ def compressed_seqlens(cu_seqlens: torch.Tensor, kernel_size: int, kernel_stride
     seqlens = (cu_seqlens[1:] - cu_seqlens[:-1]).to(torch.int64)
     y = torch.div(seqlens - kernel_size, kernel_stride, rounding_mode="floor") + 1
     y = torch.where(seqlens < kernel_size, torch.zeros_like(y), y)
-    y_cu = torch.zeros(y.numel() + 1, dtype=torch.int32)
+    y_cu = torch.zeros(y.numel() + 1, dtype=torch.int32, device=cu_seqlens.device)
     y_cu[1:] = torch.cumsum(y, 0).to(torch.int32)
     return y.to(torch.int32), y_cu
 
@@ -152,7 +152,7 @@ def select_topk_blocks(block_score, q_block, topk, init_blocks, local_blocks):
     native_sparse_attention/ops/triton/compressed_attention.py:1092-1100,1289-1292.
     """
     nb = block_score.shape[-1]
-    b_idx = torch.arange(nb)
+    b_idx = torch.arange(nb, device=block_score.device)
     forced = (b_idx[None, :] < init_blocks) | (
         (q_block[:, None] >= b_idx[None, :]) & (q_block[:, None] < b_idx[None, :] + local_blocks)
     )
@@ -161,6 +161,55 @@ def select_topk_blocks(block_score, q_block, topk, init_blocks, local_blocks):
     idx = s.topk(k, dim=-1).indices.sort(-1).values
     idx = torch.where(idx > q_block[:, None], torch.full_like(idx, -1), idx)
     return idx.to(torch.int32), s
+
+
+# --------------------------------------------------------------------------- #
+# masked attention core: one KV head and one chunk of query rows at a time
+# --------------------------------------------------------------------------- #
+QUERY_CHUNK = 1024  # rows of logits held at once: [G, QUERY_CHUNK, Lk] fp32 per step
+
+
+def _chunk_attention(qc, kh, vh, mask, sm_scale):
+    """qc [c, G, d], kh/vh [Lk, d], mask bool [c, Lk] -> (out [c, G, d], p [G, c, Lk]); rows with no key give 0."""
+    logits = torch.einsum("qgd,kd->gqk", qc, kh) * sm_scale
+    logits = logits.masked_fill(~mask[None], float("-inf"))
+    p = logits.softmax(-1).nan_to_num(0)
+    return torch.einsum("gqk,kd->qgd", p, vh), p
+
+
+def _masked_attention(q_seq, k_seq, v_seq, mask_fn, sm_scale, score_fn=None):
+    """Softmax attention of one sequence with an arbitrary mask, evaluated per KV head and per chunk of QUERY_CHUNK
+    query rows so that the memory in use is linear in the key length per chunk; chunks are re-evaluated in the
+    backward pass (torch.utils.checkpoint) instead of being kept, so gradients cost no more memory than outputs.
+
+    q_seq [Lq, Hq, d], k_seq/v_seq [Lk, Hkv, d] (any float dtype, any device); mask_fn(h, t0, t1) -> bool [t1-t0, Lk] for
+    KV head h; score_fn(h, t0, t1, p_sum [t1-t0, Lk]) receives the probabilities summed over the head's query group.
+    Returns fp32 [Lq, Hq, d]."""
+    from torch.utils.checkpoint import checkpoint
+
+    Lq, Hq, d = q_seq.shape
+    Hkv = k_seq.shape[1]
+    G = Hq // Hkv
+    qf, kf, vf = q_seq.float(), k_seq.float(), v_seq.float()
+    need_grad = torch.is_grad_enabled() and (qf.requires_grad or kf.requires_grad or vf.requires_grad)
+    heads = []
+    for h in range(Hkv):
+        rows = []
+        for t0 in range(0, Lq, QUERY_CHUNK):
+            t1 = min(Lq, t0 + QUERY_CHUNK)
+            qc, kh, vh = qf[t0:t1, h * G:(h + 1) * G], kf[:, h], vf[:, h]
+            mask = mask_fn(h, t0, t1)
+            if score_fn is not None:
+                with torch.no_grad():
+                    score_fn(h, t0, t1, _chunk_attention(qc, kh, vh, mask, sm_scale)[1].sum(0))
+            if need_grad:
+                out = checkpoint(lambda a, b, c, m=mask: _chunk_attention(a, b, c, m, sm_scale)[0], qc, kh, vh,
+                                 use_reentrant=False)
+            else:
+                out = _chunk_attention(qc, kh, vh, mask, sm_scale)[0]
+            rows.append(out)
+        heads.append(torch.cat(rows, 0) if rows else qf.new_zeros(0, G, d))
+    return torch.cat(heads, 1) if heads else qf.new_zeros(Lq, Hq, d)
 
 
 # --------------------------------------------------------------------------- #
@@ -184,36 +233,37 @@ def compressed_attention(
     """
     N, Hq, d = q.shape
     Hkv = k.shape[1]
-    G = Hq // Hkv
+    dev = q.device
     B = cu_seqlens_q.numel() - 1
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(d)
-    seqlens_q = (cu_seqlens_q[1:] - cu_seqlens_q[:-1]).tolist()
+    cu_q, cu_k = cu_seqlens_q.tolist(), cu_seqlens_k.tolist()
+    seqlens_q = [cu_q[b + 1] - cu_q[b] for b in range(B)]
     if max_seqlen_q is None:
         max_seqlen_q = max(seqlens_q)
     num_blocks = math.ceil(max_seqlen_q / block_size)
     outs, idxs, scores = [], [], []
     for b in range(B):
-        qs, qe = int(cu_seqlens_q[b]), int(cu_seqlens_q[b + 1])
-        ks_, ke = int(cu_seqlens_k[b]), int(cu_seqlens_k[b + 1])
+        qs, qe, ks_, ke = cu_q[b], cu_q[b + 1], cu_k[b], cu_k[b + 1]
         Lq, Lk = qe - qs, ke - ks_
-        qb = q[qs:qe].float()
-        kb = k[ks_:ke].float().repeat_interleave(G, 1)
-        vb = v[ks_:ke].float().repeat_interleave(G, 1)
-        t = torch.arange(Lq)
-        kmax = torch.arange(Lk) * kernel_stride + kernel_size - 1
-        mask = t[:, None] >= kmax[None, :]
-        logits = torch.einsum("qhd,khd->hqk", qb, kb) * sm_scale
-        logits = logits.masked_fill(~mask[None], float("-inf"))
-        p = logits.softmax(-1).nan_to_num(0)
-        outs.append(torch.einsum("hqk,khd->qhd", p, vb))
-        if topk > 0:
-            with torch.no_grad():
-                sc = p.reshape(Hkv, G, Lq, Lk).sum(1)
-                bsc = block_scores_from_key_scores(sc, kernel_size, kernel_stride, block_size, num_blocks)
-                idx, forced_sc = select_topk_blocks(bsc, t // block_size, topk, init_blocks, local_blocks)
-                idxs.append(idx)
-                scores.append(forced_sc)
+        kmax = torch.arange(Lk, device=dev) * kernel_stride + kernel_size - 1
+        t_all = torch.arange(Lq, device=dev)
+        idx_b = torch.empty(Hkv, Lq, min(topk, num_blocks) if topk > 0 else 0, dtype=torch.int32, device=dev)
+        sc_b = torch.empty(Hkv, Lq, num_blocks, device=dev) if (topk > 0 and return_scores) else None
+
+        def mask_fn(h, t0, t1):
+            return t_all[t0:t1, None] >= kmax[None, :]
+
+        def score_fn(h, t0, t1, p_sum):
+            bsc = block_scores_from_key_scores(p_sum, kernel_size, kernel_stride, block_size, num_blocks)
+            idx, forced_sc = select_topk_blocks(bsc, t_all[t0:t1] // block_size, topk, init_blocks, local_blocks)
+            idx_b[h, t0:t1] = idx
+            if sc_b is not None:
+                sc_b[h, t0:t1] = forced_sc
+
+        outs.append(_masked_attention(q[qs:qe], k[ks_:ke], v[ks_:ke], mask_fn, sm_scale, score_fn if topk > 0 else None))
+        idxs.append(idx_b)
+        scores.append(sc_b)
     o = torch.cat(outs, 0).to(q.dtype)
     if topk <= 0:
         return (o, None, None) if return_scores else (o, None)
@@ -235,28 +285,27 @@ def topk_sparse_attention(q, k, v, topk_idx, block_size, cu_seqlens, softmax_sca
     validity rule of ops/triton/topk_sparse_attention.py:89-93,138.
     """
     N, Hq, d = q.shape
-    Hkv = k.shape[1]
-    G = Hq // Hkv
+    dev = q.device
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(d)
-    B = cu_seqlens.numel() - 1
+    cu = cu_seqlens.tolist()
     outs = []
-    for b in range(B):
-        s, e = int(cu_seqlens[b]), int(cu_seqlens[b + 1])
+    for b in range(len(cu) - 1):
+        s, e = cu[b], cu[b + 1]
         L = e - s
         nb = math.ceil(L / block_size)
-        t = torch.arange(L)
-        idx = topk_idx[:, s:e].long()  # [Hkv, L, T]
-        valid = (idx >= 0) & (idx <= (t // block_size)[None, :, None])
-        sel = torch.zeros(Hkv, L, nb + 1, dtype=torch.bool)
-        sel.scatter_(2, torch.where(valid, idx, torch.full_like(idx, nb)), True)
-        sel = sel[..., :nb]
-        mask = sel.repeat_interleave(block_size, 2)[..., :L] & (t[None, :, None] >= t[None, None, :])
-        mask = mask.repeat_interleave(G, 0)
-        logits = torch.einsum("qhd,khd->hqk", q[s:e].float(), k[s:e].float().repeat_interleave(G, 1))
-        logits = (logits * softmax_scale).masked_fill(~mask, float("-inf"))
-        p = logits.softmax(-1).nan_to_num(0)
-        outs.append(torch.einsum("hqk,khd->qhd", p, v[s:e].float().repeat_interleave(G, 1)))
+        t_all = torch.arange(L, device=dev)
+        idx_seq = topk_idx[:, s:e].long().to(dev)  # [Hkv, L, T]
+
+        def mask_fn(h, t0, t1):
+            t = t_all[t0:t1]
+            idx = idx_seq[h, t0:t1]
+            valid = (idx >= 0) & (idx <= (t // block_size)[:, None])
+            sel = torch.zeros(t1 - t0, nb + 1, dtype=torch.bool, device=dev)
+            sel.scatter_(1, torch.where(valid, idx, torch.full_like(idx, nb)), True)
+            return sel[:, :nb].repeat_interleave(block_size, 1)[:, :L] & (t[:, None] >= t_all[None, :])
+
+        outs.append(_masked_attention(q[s:e], k[s:e], v[s:e], mask_fn, softmax_scale))
     return torch.cat(outs, 0).to(q.dtype)
 
 
@@ -270,19 +319,20 @@ def flash_attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q=Non
     Follows native_sparse_attention/ops/triton/flash_attention.py:118-131.
     """
     N, Hq, d = q.shape
-    G = Hq // k.shape[1]
+    dev = q.device
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(d)
+    cu_q, cu_k = cu_seqlens_q.tolist(), cu_seqlens_k.tolist()
     outs = []
-    for b in range(cu_seqlens_q.numel() - 1):
-        qs, qe = int(cu_seqlens_q[b]), int(cu_seqlens_q[b + 1])
-        ks_, ke = int(cu_seqlens_k[b]), int(cu_seqlens_k[b + 1])
-        logits = torch.einsum("qhd,khd->hqk", q[qs:qe].float(), k[ks_:ke].float().repeat_interleave(G, 1)) * sm_scale
-        if causal:
-            m = torch.arange(qe - qs)[:, None] >= torch.arange(ke - ks_)[None, :]
-            logits = logits.masked_fill(~m[None], float("-inf"))
-        p = logits.softmax(-1).nan_to_num(0)
-        outs.append(torch.einsum("hqk,khd->qhd", p, v[ks_:ke].float().repeat_interleave(G, 1)))
+    for b in range(len(cu_q) - 1):
+        qs, qe, ks_, ke = cu_q[b], cu_q[b + 1], cu_k[b], cu_k[b + 1]
+        j = torch.arange(ke - ks_, device=dev)
+
+        def mask_fn(h, t0, t1):
+            i = torch.arange(t0, t1, device=dev)
+            return (i[:, None] >= j[None, :]) if causal else torch.ones(t1 - t0, ke - ks_, dtype=torch.bool, device=dev)
+
+        outs.append(_masked_attention(q[qs:qe], k[ks_:ke], v[ks_:ke], mask_fn, sm_scale))
     return torch.cat(outs, 0).to(q.dtype)
 
 
@@ -292,23 +342,24 @@ def sliding_window_attention(q, k, v, cu_seqlens, window_size, sm_scale=None):
     The reference delegates this branch to the third-party flash_attn package
     (native_sparse_attention/module/native_sparse_attention.py:213-223, ``causal=True``,
     ``window_size=(window_size, -1)``); this restates flash_attn's published mask semantics for equal query and key
-    lengths (key j visible iff i - left <= j <= i).  Parity unpinned by the reference's own tests (it stores no
-    vectors for this branch); the GPU tests compare against this function only.
+    lengths (key j visible iff i - left <= j <= i).  Pinned by tests/golden/box_window.npz, the output of
+    flash_attn.flash_attn_varlen_func itself on a B200 (made by tests/golden/make_golden_on_box.py).
     """
     N, Hq, d = q.shape
-    G = Hq // k.shape[1]
+    dev = q.device
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(d)
+    cu = cu_seqlens.tolist()
     outs = []
-    for b in range(cu_seqlens.numel() - 1):
-        s, e = int(cu_seqlens[b]), int(cu_seqlens[b + 1])
-        logits = torch.einsum("qhd,khd->hqk", q[s:e].float(), k[s:e].float().repeat_interleave(G, 1)) * sm_scale
-        i = torch.arange(e - s)[:, None]
-        j = torch.arange(e - s)[None, :]
-        m = (j <= i) & (j >= i - window_size)
-        logits = logits.masked_fill(~m[None], float("-inf"))
-        p = logits.softmax(-1).nan_to_num(0)
-        outs.append(torch.einsum("hqk,khd->qhd", p, v[s:e].float().repeat_interleave(G, 1)))
+    for b in range(len(cu) - 1):
+        s, e = cu[b], cu[b + 1]
+        j = torch.arange(e - s, device=dev)
+
+        def mask_fn(h, t0, t1):
+            i = torch.arange(t0, t1, device=dev)[:, None]
+            return (j[None, :] <= i) & (j[None, :] >= i - window_size)
+
+        outs.append(_masked_attention(q[s:e], k[s:e], v[s:e], mask_fn, sm_scale))
     return torch.cat(outs, 0).to(q.dtype)
 
 
@@ -405,8 +456,8 @@ def compare_topk_idx(idx_test: torch.Tensor, idx_ref: torch.Tensor, ref_scores: 
     """
     H, Q, T = idx_ref.shape
     nb = ref_scores.shape[-1]
-    a = torch.zeros(H, Q, nb + 1, dtype=torch.bool)
-    b = torch.zeros(H, Q, nb + 1, dtype=torch.bool)
+    a = torch.zeros(H, Q, nb + 1, dtype=torch.bool, device=idx_ref.device)
+    b = torch.zeros(H, Q, nb + 1, dtype=torch.bool, device=idx_ref.device)
     a.scatter_(2, torch.where(idx_test >= 0, idx_test.long(), torch.full_like(idx_test, nb).long()), True)
     b.scatter_(2, torch.where(idx_ref >= 0, idx_ref.long(), torch.full_like(idx_ref, nb).long()), True)
     a, b = a[..., :nb], b[..., :nb]
