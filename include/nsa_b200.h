@@ -118,9 +118,11 @@ int nsa_flash_attn_decode(const void* q, const void* k, const void* v, const int
  * allocation can imply).  It has no counterpart in the reference.  The split-KV scratch is an 8 MiB array
  * inside the library's device image (held by every GPU that loads the library, until the process exits);
  * the caller passes inputs and the output only.  No cudaMalloc/cudaFree or allocating routine is called.
- *   num_splits: 0 = library default (nsa_decode_num_splits); the call needs
+ *   num_splits: 0 = the library chooses (nsa_decode_num_splits, lowered until the partial results fit the array, so
+ *       this never fails for size); > 0 = that many (at most 64, at most one per 64-key tile): the call then needs
  *       batch*num_kv_heads*splits*16*(head_dim+2) floats and returns -3 when that exceeds
  *       nsa_flash_attn_decode_static_capacity() floats -- ask for fewer splits (1 needs none).
+ *   The first call on a device may come from any host thread (the address lookup is serialised).
  *   The first call on a device looks up the array's device address (cudaGetSymbolAddress, once per device,
  *   with that device current): make that first call before any stream capture.
  *   All calls on a device share the one array and it keeps the previous call's contents; nothing has to be

@@ -87,126 +87,6 @@ __device__ __forceinline__ void row_delta(const T* o0, const T* o1, const uint32
 }
 
 // ------------------------------------------------------------------------------------------------
-// dense dQ
-// ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ int visible_keys_b(int t, int Lk, int window, int stride, int causal) {
-  if (!causal) return Lk;
-  if (t < window - 1) return 0;
-  return min(Lk, (t - window + 1) / stride + 1);
-}
-
-template <typename T, int D, int WARPS, int STAGES>
-__global__ void __launch_bounds__(WARPS * 32, 1)
-dense_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, DenseBwdParams p) {
-  constexpr int TILE_BYTES = kKeyTile * D * 2;
-  constexpr int PANELS = D / 64;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * 2 * TILE_BYTES);
-  uint64_t* empty = full + STAGES;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.y, h = blockIdx.z;
-  const int qs = __ldg(p.cu_q + b), Lq = __ldg(p.cu_q + b + 1) - qs;
-  const int ksq = __ldg(p.cu_k + b), Lk = __ldg(p.cu_k + b + 1) - ksq;
-  const int QPW = 16 >> p.logG;
-  const int QT = WARPS * QPW;
-  const int qt = gridDim.x - 1 - blockIdx.x;
-  const int q0 = qt * QT;
-  if (q0 >= Lq) return;
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full + s, 1);
-      mbar_init(empty + s, WARPS);
-    }
-    fence_barrier_init();
-  }
-  __syncthreads();
-  const int t_hi = min(q0 + QT, Lq) - 1;
-  const int ntiles = (visible_keys_b(t_hi, Lk, p.window, p.stride, p.causal) + kKeyTile - 1) / kKeyTile;
-  const int tw_hi = min(q0 + (warp + 1) * QPW, Lq) - 1;
-  const int my_tiles =
-      (tw_hi >= q0 + warp * QPW) ? (visible_keys_b(tw_hi, Lk, p.window, p.stride, p.causal) + kKeyTile - 1) / kKeyTile : 0;
-  auto issue = [&](int tile) {
-    const int s = tile % STAGES;
-    uint8_t* kb = smem + s * 2 * TILE_BYTES;
-    mbar_expect_tx(full + s, 2 * TILE_BYTES);
-#pragma unroll
-    for (int pn = 0; pn < PANELS; ++pn) {
-      tma_load_3d(kb + pn * (kKeyTile * 128), &tmK, full + s, pn * 64, h, ksq + tile * kKeyTile);
-      tma_load_3d(kb + TILE_BYTES + pn * (kKeyTile * 128), &tmV, full + s, pn * 64, h, ksq + tile * kKeyTile);
-    }
-  };
-  if (threadIdx.x == 0)
-    for (int i = 0; i < STAGES - 1 && i < ntiles; ++i) issue(i);
-
-  const int r_lo = lane >> 2;
-  int tq[2], nvis[2];
-  float lse2[2], delta[2];
-  long long rowoff[2];  // token / head of the two fragment rows
-  bool rok[2];
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int row = r_lo + 8 * r;
-    tq[r] = q0 + warp * QPW + (row >> p.logG);
-    rok[r] = tq[r] < Lq;
-    nvis[r] = rok[r] ? visible_keys_b(tq[r], Lk, p.window, p.stride, p.causal) : 0;
-    rowoff[r] = (long long)(qs + tq[r]) * p.Hq + h * p.G + (row & (p.G - 1));
-    lse2[r] = rok[r] ? __ldg(p.lse + rowoff[r]) : 0.f;
-  }
-  auto rowptr = [&](const void* base, long long sn, long long sh) {
-    const T* bptr = static_cast<const T*>(base) + (long long)(qs + q0 + warp * QPW) * sn + (long long)h * p.G * sh;
-    return [=](int r) -> const T* {
-      const int qi = r >> p.logG;
-      return (q0 + warp * QPW + qi < Lq) ? bptr + qi * sn + (r & (p.G - 1)) * sh : nullptr;
-    };
-  };
-  uint32_t qf[D / 16][4], dof[D / 16][4];
-  load_a_frags_global<T, D / 16>(qf, rowptr(p.q, p.q_sn, p.q_sh));
-  load_a_frags_global<T, D / 16>(dof, rowptr(p.dout, p.do_sn, p.do_sh));
-  {
-    auto orow = rowptr(p.o, p.o_sn, p.o_sh);
-    row_delta<T, D>(orow(r_lo), orow(r_lo + 8), dof, delta);
-  }
-  if ((lane & 3) == 0) {
-#pragma unroll
-    for (int r = 0; r < 2; ++r)
-      if (rok[r]) p.ld[rowoff[r]] = make_float2(lse2[r], delta[r]);
-  }
-
-  float dq[D / 8][4];
-#pragma unroll
-  for (int j = 0; j < D / 8; ++j) dq[j][0] = dq[j][1] = dq[j][2] = dq[j][3] = 0.f;
-
-  for (int i = 0; i < ntiles; ++i) {
-    const int s = i % STAGES;
-    if (threadIdx.x == 0) {
-      const int j = i + STAGES - 1;
-      if (j < ntiles) {
-        if (j >= STAGES) mbar_wait(empty + (j % STAGES), ((j / STAGES) - 1) & 1, p.st);
-        issue(j);
-      }
-    }
-    __syncwarp();
-    mbar_wait(full + s, (i / STAGES) & 1, p.st);
-    if (i < my_tiles) {
-      const uint32_t kb = smem_u32(smem + s * 2 * TILE_BYTES);
-      const int lim[2] = {nvis[0] - i * kKeyTile, nvis[1] - i * kKeyTile};
-      dq_tile<T, D>(qf, dof, dq, kb, kb + TILE_BYTES, lim, lse2, delta, p.scale2, p.sm_scale);
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(empty + s);
-  }
-  __syncthreads();
-  T* stage = reinterpret_cast<T*>(smem + warp * (16 * (D + 8) * 2));
-  T* dbase = static_cast<T*>(p.dq) + (long long)(qs + q0 + warp * QPW) * p.dq_sn + (long long)h * p.G * p.dq_sh;
-  const float one[2] = {1.f, 1.f};
-  store_rows_staged<T, D>(dq, one, stage, [&](int r) -> T* {
-    const int qi = r >> p.logG;
-    return (q0 + warp * QPW + qi < Lq) ? dbase + qi * p.dq_sn + (r & (p.G - 1)) * p.dq_sh : nullptr;
-  });
-}
-
-// ------------------------------------------------------------------------------------------------
 // sparse dQ
 // ------------------------------------------------------------------------------------------------
 struct SparseBwdParams {
@@ -691,12 +571,6 @@ __global__ void convert_rows_kernel(const float* __restrict__ src, void* dst, lo
   *reinterpret_cast<uint2*>(static_cast<T*>(dst) + n * d_sn + (long long)h * d_sh + c * 4) = out;
 }
 
-// NSA_B200_LEGACY_MMA=1 keeps the mma.sync kernels selectable for A/B measurements
-static bool legacy_mma() {
-  static const bool v = [] { const char* e = getenv("NSA_B200_LEGACY_MMA"); return e && e[0] == '1'; }();
-  return v;
-}
-
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 template <typename T, int D, bool SPARSE>
@@ -757,29 +631,11 @@ static int run_dense_bwd(const void* q, const void* k, const void* v, const void
   p.window = window; p.stride = stride; p.causal = causal; p.left = left;
   p.scale2 = sm_scale * kLog2e; p.sm_scale = sm_scale;
   p.st.word = status_word();
-  if (left >= 0 && (legacy_mma() || D != 128)) return kUnsupported;  // the sliding window lives in the tcgen05 kernels only
-  if (!legacy_mma()) {
+  if (left >= 0 && D != 128) return kUnsupported;  // the sliding window needs the tcgen05 dK/dV pass (head_dim 128)
+  {
     const int dt = DT<T>::kTmapType == CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 ? NSA_DTYPE_BF16 : NSA_DTYPE_FP16;
     const int rc = dense_dq_tc(k, v, S[2], S[3], S[4], S[5], total_q, total_k, max_q, D, dt, p, stream);
     if (rc) return rc;
-  } else
-  {
-    constexpr int WARPS = 8;
-    constexpr int STAGES = (D == 128) ? 4 : 6;
-    constexpr int TILE_BYTES = kKeyTile * D * 2;
-    CUtensorMap tmK, tmV;
-    int rc = make_tmap_3d(&tmK, DT<T>::kTmapType, k, D, Hkv, total_k, S[3], S[2], 64, 1, kKeyTile);
-    if (rc) return rc;
-    rc = make_tmap_3d(&tmV, DT<T>::kTmapType, v, D, Hkv, total_k, S[5], S[4], 64, 1, kKeyTile);
-    if (rc) return rc;
-    const size_t smem = 1024 + STAGES * 2 * TILE_BYTES + 2 * STAGES * sizeof(uint64_t);
-    auto kern = dense_dq_kernel<T, D, WARPS, STAGES>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return cuda_rc(e);
-    const int QT = WARPS * (16 / G);
-    dim3 grid((max_q + QT - 1) / QT, batch, Hkv);
-    { LaunchScope ls_("dense_dq", stream); kern<<<grid, WARPS * 32, smem, stream>>>(tmK, tmV, p); }
-    if ((e = cudaGetLastError()) != cudaSuccess) return cuda_rc(e);
   }
   DkdvParams d;
   d.ld = ld; d.dk32 = dk32; d.dv32 = dv32; d.cu_q = cu_q; d.cu_k = cu_k;
@@ -794,10 +650,7 @@ static int run_dense_bwd(const void* q, const void* k, const void* v, const void
   dim3 grid((max_k + kKeyTile - 1) / kKeyTile, (max_q + chunk - 1) / chunk, batch * Hkv);
   int rc;
   if constexpr (D == 128) {
-    if (legacy_mma())
-      rc = launch_dkdv<T, D, false>(q, dout, k, v, ds, total_q, total_k, grid, d, stream);
-    else
-      rc = launch_dense_dkdv_tc<T>(q, dout, k, v, ds, total_q, total_k, max_q, max_k, batch, d, stream);
+    rc = launch_dense_dkdv_tc<T>(q, dout, k, v, ds, total_q, total_k, max_q, max_k, batch, d, stream);
   } else {
     rc = launch_dkdv<T, D, false>(q, dout, k, v, ds, total_q, total_k, grid, d, stream);
   }
@@ -907,7 +760,7 @@ static int run_sparse_bwd(const void* q, const void* k, const void* v, const voi
   dim3 grid((unsigned)max_items, block_size / kKeyTile, 1);
   int rc;
   if constexpr (D == 128) {
-    rc = (G >= 4 && (G & (G - 1)) == 0 && !legacy_mma()) ? launch_sparse_dkdv_tc<T>(q, dout, k, v, ds, N, grid, d, stream)
+    rc = (G >= 4 && (G & (G - 1)) == 0) ? launch_sparse_dkdv_tc<T>(q, dout, k, v, ds, N, grid, d, stream)
                                                          : launch_dkdv<T, D, true>(q, dout, k, v, ds, N, N, grid, d, stream);
   } else {
     rc = launch_dkdv<T, D, true>(q, dout, k, v, ds, N, N, grid, d, stream);

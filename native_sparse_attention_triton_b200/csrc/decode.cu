@@ -15,9 +15,12 @@
 #include "nsa_b200.h"
 #include "topk_select.cuh"
 
+#include <mutex>
+
 namespace nsa {
 
 constexpr int kMaxTilesPerDecodeQuery = 64;
+constexpr int kMaxDecodeSplits = 64;  // the combine kernel handles at most 64 partial results per row
 
 struct DecodeParams {
   const void* q;
@@ -323,12 +326,12 @@ cmp_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     obase[(long long)g * p.o_sh + c] = DT<T>::from_float(dn > 0.f ? num / dn : 0.f);
   }
   if (!p.topk_idx) return;
-  __syncthreads();  // osum fully consumed before the tile buffers are refilled
+  fence_proxy_async();  // the tile buffers were overlaid with ordinary stores (osum): every warp orders its own accesses
+  __syncthreads();      // before the barrier, so that all of them precede the TMA refills issued after it
 
   // ---- pass 2: key scores = sum over heads of exp2(s - lse) ----
   float lse2[2] = {lse_sh[r0], lse_sh[r0 + 8]};
   const bool rv0 = r0 < p.G, rv1 = (r0 + 8) < p.G;
-  fence_proxy_async();  // the tile buffers were overlaid with ordinary stores (osum) before TMA refills them
   if (my_tiles > 0 && lane == 0) issue(false, warp * kKeyTile);
   for (int i = 0; i < my_tiles; ++i) {
     const int kpos = (warp + i * WARPS) * kKeyTile;
@@ -417,7 +420,7 @@ extern "C" int nsa_decode_num_splits(int batch, int num_kv_heads, int max_tiles)
   if (pairs <= 0 || max_tiles <= 1) return 1;
   int s = (148 * 6 + pairs - 1) / pairs;
   if (s > max_tiles) s = max_tiles;
-  if (s > 64) s = 64;
+  if (s > nsa::kMaxDecodeSplits) s = nsa::kMaxDecodeSplits;
   return s < 1 ? 1 : s;
 }
 
@@ -438,7 +441,7 @@ extern "C" int nsa_flash_attn_decode(const void* q, const void* k, const void* v
   p.B = batch; p.Hq = num_q_heads; p.Hkv = num_kv_heads; p.G = num_q_heads / num_kv_heads; p.T = 0; p.block_size = kKeyTile;
   const int max_tiles = (cache_len + kKeyTile - 1) / kKeyTile;
   p.S = num_splits < 1 ? 1 : (num_splits > max_tiles ? max_tiles : num_splits);
-  if (p.S > 64) p.S = 64;  // the combine kernel handles at most 64 partial results per row
+  if (p.S > kMaxDecodeSplits) p.S = kMaxDecodeSplits;
   p.tiles_per_split = (max_tiles + p.S - 1) / p.S;
   const long long need = p.S > 1 ? (long long)batch * num_kv_heads * p.S * 16 * (head_dim + 2) : 0;
   if (need > 0 && (!scratch || scratch_floats < need)) return kWorkspace;
@@ -468,7 +471,7 @@ extern "C" int nsa_topk_sparse_attn_decode(const void* q, const void* k, const v
   p.B = batch; p.Hq = num_q_heads; p.Hkv = num_kv_heads; p.G = num_q_heads / num_kv_heads; p.T = topk; p.block_size = block_size;
   const int max_tiles = topk * (block_size / kKeyTile);
   p.S = num_splits < 1 ? 1 : (num_splits > max_tiles ? max_tiles : num_splits);
-  if (p.S > 64) p.S = 64;  // the combine kernel handles at most 64 partial results per row
+  if (p.S > kMaxDecodeSplits) p.S = kMaxDecodeSplits;
   p.tiles_per_split = (max_tiles + p.S - 1) / p.S;
   const long long need = p.S > 1 ? (long long)batch * num_kv_heads * p.S * 16 * (head_dim + 2) : 0;
   if (need > 0 && (!scratch || scratch_floats < need)) return kWorkspace;
@@ -528,12 +531,14 @@ static __device__ __align__(256) float g_decode_scratch[kStaticScratchFloats];
 // handle for the runtime, not an address a kernel can use; the address comes from cudaGetSymbolAddress,
 // asked once per device with that device current.
 static float* g_decode_scratch_ptr[64] = {};
+static std::mutex g_decode_scratch_mutex;  // two host threads may make the first call on a device at the same time
 
 static int static_scratch(float** out) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_rc(e);
   if (dev < 0 || dev >= 64) return kUnsupported;
+  std::lock_guard<std::mutex> lock(g_decode_scratch_mutex);
   if (!g_decode_scratch_ptr[dev]) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_decode_scratch);
@@ -556,9 +561,14 @@ extern "C" int nsa_flash_attn_decode_static(const void* q, const void* k, const 
   if (batch <= 0 || cache_len <= 0 || num_kv_heads <= 0 || head_dim <= 0) return kInvalid;
   const int max_tiles = (cache_len + kKeyTile - 1) / kKeyTile;
   int splits = num_splits > 0 ? num_splits : nsa_decode_num_splits(batch, num_kv_heads, max_tiles);
+  // the same clamps nsa_flash_attn_decode applies, so that the capacity check sees the split count that will run
   if (splits > max_tiles) splits = max_tiles;
-  const long long need = splits > 1 ? (long long)batch * num_kv_heads * splits * 16 * (head_dim + 2) : 0;
-  if (need > kStaticScratchFloats) return kWorkspace;  // the problem does not fit the built-in scratch: use fewer splits
+  if (splits > kMaxDecodeSplits) splits = kMaxDecodeSplits;
+  const long long per_split = (long long)batch * num_kv_heads * 16 * (head_dim + 2);
+  if (num_splits <= 0)  // the library's own choice: take the largest split count whose partials fit (1 needs none)
+    while (splits > 1 && per_split * splits > kStaticScratchFloats) --splits;
+  const long long need = splits > 1 ? per_split * splits : 0;
+  if (need > kStaticScratchFloats) return kWorkspace;  // an explicit split count that does not fit: ask for fewer
   float* scratch = nullptr;
   const int rc = static_scratch(&scratch);
   if (rc) return rc;

@@ -231,16 +231,13 @@ extern "C" int nsa_compressed_attn_topk(const void* q, const void* k, const floa
   p.st.word = status_word();
   if ((p.q_sn | p.q_sh) % 8 || !aligned16(q)) return kInvalid;
   {
-    static const bool legacy = [] { const char* e = getenv("NSA_B200_LEGACY_MMA"); return e && e[0] == '1'; }();
-    if (!legacy) {
-      // two row tiles per CTA when their block scores fit in shared memory, else one, else the mma.sync kernel
-      int rc = score_topk_pp_tc(q, k, strides[2], strides[3], total_q, total_k, max_seqlen_q, head_dim, dtype, p,
-                                static_cast<cudaStream_t>(stream));
-      if (rc == kUnsupported)
-        rc = score_topk_tc(q, k, strides[2], strides[3], total_q, total_k, max_seqlen_q, head_dim, dtype, p,
-                           static_cast<cudaStream_t>(stream));
-      if (rc != kUnsupported) return rc;
-    }
+    // two row tiles per CTA when their block scores fit in shared memory, else one, else the mma.sync kernel (G < 4)
+    int rc = score_topk_pp_tc(q, k, strides[2], strides[3], total_q, total_k, max_seqlen_q, head_dim, dtype, p,
+                              static_cast<cudaStream_t>(stream));
+    if (rc == kUnsupported)
+      rc = score_topk_tc(q, k, strides[2], strides[3], total_q, total_k, max_seqlen_q, head_dim, dtype, p,
+                         static_cast<cudaStream_t>(stream));
+    if (rc != kUnsupported) return rc;
   }
   return NSA_DISPATCH_T_D(dtype, head_dim, launch_score_topk, k, strides[2], strides[3], total_k, max_seqlen_q, p,
                           static_cast<cudaStream_t>(stream));

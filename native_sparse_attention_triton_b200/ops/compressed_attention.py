@@ -106,7 +106,7 @@ def compressed_attention(
         warnings.warn("topk <= 0, returned topk_idx will be None")
         return attn_output, None
     assert topk >= init_blocks + local_blocks
-    assert block_size % kernel_size == 0 and kernel_size % kernel_stride == 0
+    assert block_size % kernel_stride == 0 and kernel_size % kernel_stride == 0
     with torch.no_grad():
         if sm_scale is None:
             sm_scale = default_scale(q.shape[-1])

@@ -67,5 +67,9 @@ def topk_sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, top
     """
     require_cuda(q, k, v, topk_idx, cu_seqlens)
     assert block_size in {32, 64, 128, 256}
+    if block_size == 32:
+        raise NotImplementedError("block_size 32 is not built: the kernels work on 64-key tiles (use 64, 128 or 256)")
+    if topk_idx.shape[-1] * (block_size // 64) > 64:
+        raise NotImplementedError("at most 64 tiles of 64 keys per query (topk * block_size / 64 <= 64)")
     assert q.shape[1] % k.shape[1] == 0 and k.shape[1] == v.shape[1] and k.shape[1] == topk_idx.shape[0]
     return TopkSparseAttention.apply(q, k, v, topk_idx, block_size, cu_seqlens, softmax_scale)

@@ -376,7 +376,7 @@ def flash_attention_decode(q, k, v, seqlens, sm_scale=None):
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(d)
     L = k.shape[1]
-    mask = torch.arange(L)[None, :] < seqlens[:, None]
+    mask = torch.arange(L, device=q.device)[None, :] < seqlens[:, None]
     logits = torch.einsum("bhd,bjhd->bhj", q.float(), k.float().repeat_interleave(G, 2)) * sm_scale
     logits = logits.masked_fill(~mask[:, None, :], float("-inf"))
     p = logits.softmax(-1).nan_to_num(0)
@@ -399,9 +399,9 @@ def compressed_attention_decode(q, k, v, seqlens, compress_seqlens, kernel_size,
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(d)
     if Lc == 0:
-        res = (torch.zeros_like(q), torch.zeros(Hkv, B, 1, dtype=torch.int32))
+        res = (torch.zeros_like(q), torch.zeros(Hkv, B, 1, dtype=torch.int32, device=q.device))
         return res + (None,) if return_scores else res
-    mask = torch.arange(Lc)[None, :] < compress_seqlens[:, None]
+    mask = torch.arange(Lc, device=q.device)[None, :] < compress_seqlens[:, None]
     logits = torch.einsum("bhd,bjhd->bhj", q.float(), k.float().repeat_interleave(G, 2)) * sm_scale
     logits = logits.masked_fill(~mask[:, None, :], float("-inf"))
     p = logits.softmax(-1).nan_to_num(0)
@@ -430,10 +430,10 @@ def topk_sparse_attention_decode(q, k, v, topk_idx, block_size, seqlens, sm_scal
     nb = math.ceil(L / block_size)
     idx = topk_idx.long()  # [Hkv, B, T]
     valid = (idx >= 0) & (idx <= ((seqlens.long() - 1) // block_size)[None, :, None])
-    sel = torch.zeros(Hkv, B, nb + 1, dtype=torch.bool)
+    sel = torch.zeros(Hkv, B, nb + 1, dtype=torch.bool, device=q.device)
     sel.scatter_(2, torch.where(valid, idx, torch.full_like(idx, nb)), True)
     mask = sel[..., :nb].repeat_interleave(block_size, 2)[..., :L]
-    mask = mask & (torch.arange(L)[None, None, :] < seqlens[None, :, None])
+    mask = mask & (torch.arange(L, device=q.device)[None, None, :] < seqlens[None, :, None])
     mask = mask.permute(1, 0, 2).repeat_interleave(G, 1)  # [B, Hq, L]
     logits = torch.einsum("bhd,bjhd->bhj", q.float(), k.float().repeat_interleave(G, 2)) * sm_scale
     logits = logits.masked_fill(~mask, float("-inf"))
@@ -544,8 +544,8 @@ def rope(x, inv_freq, cu_seqlens, step=0, stride=1, attention_scaling=1.0):
         pos = torch.cat([torch.arange(n) for n in lens]) if lens else torch.zeros(0, dtype=torch.long)
     else:
         pos = torch.tensor([n + step - 1 for n in lens])
-    pos = (pos * stride).float()
-    ang = inv_freq.float()[None, :] * pos[:, None]
+    pos = (pos * stride).float().to(x.device)
+    ang = inv_freq.float().to(x.device)[None, :] * pos[:, None]
     cos = (ang.cos() * attention_scaling).to(x.dtype).float()
     sin = (ang.sin() * attention_scaling).to(x.dtype).float()
     half = x.shape[-1] // 2

@@ -67,3 +67,75 @@ def padded_cache(x, cu, seqlens, pad_to=None):
     for b, L in enumerate(seqlens):
         out[b, :L] = x[int(cu[b]):int(cu[b]) + L]
     return out
+
+
+def window_case_inputs():
+    """Seeded inputs of the sliding-window fixture (tests/golden/box_window.npz)."""
+    g = torch.Generator().manual_seed(2024)
+    seqlens, Hq, Hkv, d = [37, 300, 700], 8, 2, 128
+    N = sum(seqlens)
+    cu = torch.tensor([0] + list(np.cumsum(seqlens)), dtype=torch.int32)
+    mk = lambda *s: bf16_exact(torch.randn(*s, generator=g))
+    return dict(cu=cu, q=mk(N, Hq, d), k=mk(N, Hkv, d), v=mk(N, Hkv, d), do=mk(N, Hq, d))
+
+
+def rope_case_inputs():
+    """Seeded inputs of the rotary-embedding fixture (tests/golden/box_rope.npz): a ragged batch, its compressed counterpart
+    (kernel 32, stride 16) and one decode row per sequence.  Values are exact in bf16 and in fp16."""
+    g = torch.Generator().manual_seed(77)
+    seqlens, H, d = [5, 130, 1000], 2, 128
+    clens = [0 if L < 32 else (L - 32) // 16 + 1 for L in seqlens]
+    cu = torch.tensor([0] + list(np.cumsum(seqlens)), dtype=torch.int32)
+    cu_c = torch.tensor([0] + list(np.cumsum(clens)), dtype=torch.int32)
+    mk = lambda *s: (torch.randint(-512, 513, s, generator=g).float() / 128.0)
+    return dict(cu=cu, cu_c=cu_c, x=mk(sum(seqlens), H, d), xc=mk(sum(clens), H, d), xd=mk(len(seqlens), H, d))
+
+
+INFER_PARAMS = dict(HQ=8, HKV=2, D=128, KS=32, ST=16, BS=64, TOPK=4, INIT=1, LOCAL=2, W=64, MAXLEN=512, MAXB=4)
+
+
+def infer_case_inputs(mode, lens, steps, dtype=torch.bfloat16):
+    """Seeded inputs of an inference scenario (prefill of a ragged batch, then `steps` decode steps): used by the GPU
+    inference tests and by the fixtures tests/golden/box_infer_*.npz.  All tensors are exact in `dtype`."""
+    P = INFER_PARAMS
+    HQ, HKV, D, KS = P["HQ"], P["HKV"], P["D"], P["KS"]
+    g = torch.Generator().manual_seed(100 + len(lens) + steps)
+    B, total = len(lens), sum(lens)
+    cu = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32)
+    rd = lambda t: t.to(dtype).float()
+    if mode == "linear":
+        mk = lambda: rd(torch.randn(HKV, KS * D, D, generator=g) / math.sqrt(KS * D))
+        w_k, w_v, pe = mk(), mk(), rd(torch.randn(HKV, KS, D, generator=g) * 0.02)
+    elif mode == "weighted":
+        mk = lambda: rd(torch.rand(HKV, KS, generator=g) / KS)
+        w_k, w_v, pe = mk(), mk(), rd(torch.randn(HKV, KS, D, generator=g) * 0.02)
+    else:
+        w_k = w_v = pe = None
+    rnd = lambda *s: rd(torch.randn(*s, generator=g))
+    q, k, v = rnd(total, HQ, D), rnd(total, HKV, D), rnd(total, HKV, D)
+    gate = rd(torch.rand(total, HQ, 3, generator=g))
+    step_inputs = []
+    for _ in range(steps):
+        qn, kn, vn = rnd(B, HQ, D), rnd(B, HKV, D), rnd(B, HKV, D)
+        step_inputs.append((qn, kn, vn, rd(torch.rand(B, HQ, 3, generator=g))))
+    return dict(params=P, cu=cu, w_k=w_k, w_v=w_v, pe=pe, q=q, k=k, v=v, gate=gate, steps=step_inputs)
+
+
+def from_bits16(a: np.ndarray) -> torch.Tensor:
+    """uint16 fp16 bit patterns -> fp32 tensor."""
+    return torch.from_numpy(a.view(np.int16).copy()).view(torch.float16).float()
+
+
+def box_fixture(name):
+    """A fixture written by tests/golden/make_golden_on_box.py (outputs of the reference itself on a B200), or None."""
+    path = os.path.join(GOLDEN_DIR, name + ".npz")
+    return np.load(path) if os.path.exists(path) else None
+
+
+def close_16bit(test, ref, max_tol=2e-2, mean_tol=2e-3):
+    """(ok, max error relative to max(1, |ref|), mean absolute error): the acceptance rule of the hot path for 16-bit
+    results of unit-variance problems."""
+    t, r = test.float().cpu(), ref.float().cpu()
+    e = (t - r).abs()
+    mx, mean = float((e / r.abs().clamp(min=1.0)).max()), float(e.mean())
+    return (mx <= max_tol and mean <= mean_tol), mx, mean

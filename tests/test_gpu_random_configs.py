@@ -25,9 +25,6 @@ def draw(seed):
     Hkv = rnd.choice([1, 2, 4])
     G = rnd.choice([1, 2, 4, 8, 16])
     ks, st, bs = rnd.choice([(32, 16, 64), (16, 8, 64), (64, 16, 128), (32, 32, 64), (16, 16, 64), (64, 32, 128), (32, 8, 64)])
-    a, c = ks // st, bs // st
-    if a + c - 1 > 8:   # the score kernels fold at most 8 taps
-        ks, st, bs = 32, 16, 64
     nseq = rnd.choice([1, 2, 3, 5])
     seqlens = [rnd.choice([rnd.randint(1, 40), rnd.randint(60, 700), rnd.randint(700, 1500)]) for _ in range(nseq)]
     topk = rnd.choice([3, 4, 8, 16])

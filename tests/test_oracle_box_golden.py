@@ -1,0 +1,120 @@
+"""Pins of the CPU oracle against outputs of the REFERENCE ITSELF run on a B200 (tests/golden/box_*.npz, written by
+tests/golden/make_golden_on_box.py): the reference's Triton operators, flash_attn's sliding-window call, the reference's
+RotaryEmbedding, and its nsa_infer + NSACache over a prefill and a run of decode steps.  No GPU is needed here."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import nsa_oracle as O
+from tests.helpers import (box_fixture, chain_inputs, close_16bit, from_bits, from_bits16, infer_case_inputs,
+                           rope_case_inputs, window_case_inputs)
+
+
+def need(name):
+    z = box_fixture(name)
+    if z is None:
+        pytest.skip(f"tests/golden/{name}.npz has not been generated")
+    return z
+
+
+@pytest.mark.parametrize("name", ["box_triton_cfg1", "box_triton_g16_d128"])
+def test_oracle_matches_reference_triton_chain(name):
+    z = need(name)
+    m = {k: (z[k].tolist() if z[k].ndim else z[k].item()) for k in ("seed", "seqlens", "Hq", "Hkv", "d", "ks", "st", "bs", "topk",
+                                                                    "init_blocks", "local_blocks", "row_step")}
+    inp = chain_inputs(m["seed"], m["seqlens"], m["Hq"], m["Hkv"], m["d"], m["ks"])
+    assert abs(float(inp["q"].double().sum()) - float(z["q_sum"])) < 1e-6
+    g = torch.Generator().manual_seed(m["seed"] + 1000)
+    N = sum(m["seqlens"])
+    do_cmp = torch.randn(N, m["Hq"], m["d"], generator=g).bfloat16().float()
+    do_sel = torch.randn(N, m["Hq"], m["d"], generator=g).bfloat16().float()
+    t = {n: inp[n].clone().requires_grad_(True) for n in ("q", "k", "v", "wk", "wv", "pe")}
+    cu, rs = inp["cu"], m["row_step"]
+    ck, cu_k = O.linear_compress(t["k"], t["wk"], cu, m["ks"], m["st"], t["pe"])
+    cv, _ = O.linear_compress(t["v"], t["wv"], cu, m["ks"], m["st"], None)
+    assert torch.equal(cu_k, torch.from_numpy(z["cu_k"]).to(torch.int32))
+    for a, b in ((ck, "lin_k"), (cv, "lin_v")):
+        ok, mx, mean = close_16bit(a, from_bits(z[b]))
+        assert ok, (b, mx, mean)
+    # attention on the 16-bit compressed tensors the reference's kernels saw
+    ckr, cvr = ck.bfloat16().float(), cv.bfloat16().float()
+    ck2 = ck + (ckr - ck).detach()
+    cv2 = cv + (cvr - cv).detach()
+    o_cmp, idx, _ = O.compressed_attention(t["q"], ck2, cv2, m["ks"], m["st"], m["bs"], m["topk"], cu, cu_k,
+                                           init_blocks=m["init_blocks"], local_blocks=m["local_blocks"], return_scores=True)
+    ref_idx = torch.from_numpy(z["topk_idx"].astype(np.int32))
+    bad, differing, rows = O.compare_topk_idx(idx, ref_idx, torch.from_numpy(z["block_score"]), tie_tol=1e-3)
+    assert bad == 0, (bad, differing, rows)
+    o_sel = O.topk_sparse_attention(t["q"], t["k"], t["v"], ref_idx, m["bs"], cu)
+    torch.autograd.backward([o_cmp, o_sel], [do_cmp, do_sel])
+    checks = [(o_cmp[::rs], "o_cmp"), (o_sel[::rs], "o_sel"), (t["q"].grad[::rs], "dq"), (t["k"].grad, "dk"), (t["v"].grad, "dv"),
+              (t["wk"].grad[:, ::8], "dwk"), (t["wv"].grad[:, ::8], "dwv"), (t["pe"].grad, "dpe")]
+    for a, b in checks:
+        ok, mx, mean = close_16bit(a, from_bits(z[b]), 3e-2, 3e-3 if b.startswith("d") else 2e-3)
+        print(name, b, "max", mx, "mean", mean)
+        assert ok, (b, mx, mean)
+
+
+def test_oracle_matches_flash_attn_sliding_window():
+    z = need("box_window")
+    for W in (64, 512):
+        inp = window_case_inputs()
+        q, k, v = (inp[n].clone().requires_grad_(True) for n in ("q", "k", "v"))
+        o = O.sliding_window_attention(q, k, v, inp["cu"], W)
+        o.backward(inp["do"])
+        for a, b in ((o[::8], f"o_w{W}"), (q.grad[::8], f"dq_w{W}"), (k.grad[::4], f"dk_w{W}"), (v.grad[::4], f"dv_w{W}")):
+            ok, mx, mean = close_16bit(a, from_bits(z[b]))
+            print(b, "max", mx, "mean", mean)
+            assert ok, (b, mx, mean)
+
+
+def test_oracle_matches_reference_rotary_embedding():
+    z = need("box_rope")
+    inp = rope_case_inputs()
+    for tag in ("f8", "f4"):
+        inv_freq, scaling = torch.from_numpy(z[f"inv_freq_{tag}"]), float(z[f"scaling_{tag}"])
+        for dt, dec, dn in ((torch.bfloat16, from_bits, "bf16"), (torch.float16, from_bits16, "fp16")):
+            ulp = 2.0 ** (-8 if dn == "bf16" else -11)
+            cases = [("prefill", inp["x"], inp["cu"], 0, 1, 4), ("strided", inp["xc"], inp["cu_c"], 0, 16, 1),
+                     ("decode3", inp["xd"], inp["cu"], 3, 1, 1), ("decode1s", inp["xd"], inp["cu_c"], 1, 16, 1)]
+            for nm, x, cu, step, stride, rs in cases:
+                got = O.rope(x.to(dt), inv_freq, cu, step, stride, scaling).float()[::rs]
+                want = dec(z[f"{nm}_{tag}_{dn}"])
+                # the reference rounds both products and their sum to the tensor's dtype; the oracle rounds once
+                err = ((got - want).abs() / want.abs().clamp(min=1.0)).max()
+                assert float(err) <= 3 * ulp, (tag, dn, nm, float(err))
+
+
+@pytest.mark.parametrize("name,mode,lens,steps", [("box_infer_weighted", "weighted", [33, 200], 24),
+                                                  ("box_infer_linear", "linear", [40, 100, 300], 40)])
+def test_oracle_matches_reference_inference(name, mode, lens, steps):
+    z = need(name)
+    c = infer_case_inputs(mode, lens, steps)
+    P = c["params"]
+    inv_freq, scaling = torch.from_numpy(z["inv_freq"]), float(z["scaling"])
+    ofn = {"linear": O.linear_compress, "weighted": O.weightedpool_compress}[mode]
+    a = (P["KS"], P["ST"], P["BS"], P["TOPK"], P["INIT"], P["LOCAL"], P["W"])
+    ref = O.nsa_prefill(c["q"], c["k"], c["v"], c["gate"], c["cu"], inv_freq, ofn, ofn, c["w_k"], c["w_v"], c["pe"], *a,
+                        attention_scaling=scaling)
+    ok, mx, mean = close_16bit(ref, from_bits(z["prefill"]), 4e-2, 3e-3)
+    assert ok, ("prefill", mx, mean)
+    cu = c["cu"]
+    hist_k = [c["k"][cu[b]:cu[b + 1]] for b in range(len(lens))]
+    hist_v = [c["v"][cu[b]:cu[b + 1]] for b in range(len(lens))]
+    dec = from_bits(z["decode"])
+    off = 0
+    for step in range(1, steps + 1):
+        qn, kn, vn, gn = c["steps"][step - 1]
+        for b in range(len(lens)):
+            hist_k[b] = torch.cat([hist_k[b], kn[b:b + 1]])
+            hist_v[b] = torch.cat([hist_v[b], vn[b:b + 1]])
+            ref = O.nsa_decode_token(qn[b], hist_k[b], hist_v[b], gn[b], inv_freq, ofn, ofn, c["w_k"], c["w_v"], c["pe"], *a,
+                                     attention_scaling=scaling)
+            ok, mx, mean = close_16bit(ref, dec[step - 1, b], 4e-2, 3e-3)
+            off += not ok
+            assert mx <= 0.5, (step, b, mx, mean)
+    # a block chosen differently at a score tie moves one row; nothing else may
+    assert off <= max(1, steps * len(lens) // 25), off
+    n = torch.tensor(lens) + steps
+    assert z["sparse_len"].tolist() == n.tolist()
+    assert z["compress_len"].tolist() == [0 if x < P["KS"] else (x - P["KS"]) // P["ST"] + 1 for x in n.tolist()]

@@ -70,3 +70,25 @@ def test_static_scratch_rejects_oversized_problems():
     ref = pkg.ops.flash_attention_decode(q, k, v, seqlens)
     err = (o.float() - ref.float()).abs()
     assert float(err.max()) <= 2e-2 and float(err.mean()) <= 2e-3
+
+
+def test_static_scratch_default_split_count_always_fits():
+    """With num_splits = 0 the library picks the split count itself, so it must pick one whose partial results fit the
+    built-in array (batch 64 x 4 KV heads at head_dim 128 would want 4 splits = 2 129 920 floats, 32 768 too many); and an
+    explicit request above the 64-split limit is clamped to 64 before its size is judged, as the regular entry point does."""
+    import native_sparse_attention_triton_b200 as pkg
+
+    lib = pkg._lib.lib()
+    q, k, v, seqlens = _case(4, 64, 1024, 32, 4, 128)
+    ref = pkg.ops.flash_attention_decode(q, k, v, seqlens)
+    rc, o = _call_static(lib, q, k, v, seqlens, 0)
+    assert rc == 0
+    err = (o.float() - ref.float()).abs()
+    assert float(err.max()) <= 2e-2 and float(err.mean()) <= 2e-3
+    q, k, v, seqlens = _case(5, 1, 8192, 16, 1, 128)   # 128 tiles: 200 requested splits run as 64, 133 120 floats
+    ref = pkg.ops.flash_attention_decode(q, k, v, seqlens)
+    rc, o = _call_static(lib, q, k, v, seqlens, 200)
+    assert rc == 0
+    err = (o.float() - ref.float()).abs()
+    assert float(err.max()) <= 2e-2 and float(err.mean()) <= 2e-3
+    assert pkg.device_status() == 0
