@@ -132,10 +132,54 @@ def box_fixture(name):
     return np.load(path) if os.path.exists(path) else None
 
 
-def close_16bit(test, ref, max_tol=2e-2, mean_tol=2e-3):
-    """(ok, max error relative to max(1, |ref|), mean absolute error): the acceptance rule of the hot path for 16-bit
-    results of unit-variance problems."""
-    t, r = test.float().cpu(), ref.float().cpu()
+# ---- the acceptance rule of the hot path, in one place --------------------------------------------------------------
+# Results are compared after normalising the tensor to unit variance when its RMS exceeds 1 (outputs of N(0,1) problems
+# have RMS <= 1 and are compared in absolute terms; gradients that sum thousands of terms are not): with
+# scale = max(1, rms(ref)),
+#     max over elements of |test - ref| / max(|ref|, scale) <= MAX_TOL   (an element of magnitude m carries m * 2^-9 of
+#                                                                       16-bit rounding by itself)
+#     mean |test - ref| / scale                             <= MEAN_TOL
+# dK and dV of the two attention operators are sums, over every query row that sees a key, of products of 16-bit P / dS
+# values: their worst element is allowed KV_GRAD_MAX_TOL.  On the same seeded inputs the reference's own Triton kernels
+# score up to 0.128 there against the fp32 oracle and these kernels 0.074 (BASELINE configurations 1 and 2, measured on a
+# B200 by tests/test_gpu_vs_reference.py); every other tensor of either implementation stayed below 1.5e-2, means below
+# 1.7e-3.
+MAX_TOL, MEAN_TOL, KV_GRAD_MAX_TOL = 2e-2, 2e-3, 8e-2
+
+
+def error_16bit(test, ref):
+    """(max error, mean error, scale) of `test` against `ref` under the rule above."""
+    t, r = test.detach().float().cpu(), ref.detach().float().cpu()
+    if r.numel() == 0:
+        return 0.0, 0.0, 1.0
+    scale = max(1.0, float(r.pow(2).mean().sqrt()))
     e = (t - r).abs()
-    mx, mean = float((e / r.abs().clamp(min=1.0)).max()), float(e.mean())
+    return float((e / r.abs().clamp(min=scale)).max()), float(e.mean()) / scale, scale
+
+
+def close_16bit(test, ref, max_tol=MAX_TOL, mean_tol=MEAN_TOL):
+    """(ok, max error, mean error) under the rule above."""
+    mx, mean, _ = error_16bit(test, ref)
     return (mx <= max_tol and mean <= mean_tol), mx, mean
+
+
+def assert_close_16bit(test, ref, what, max_tol=MAX_TOL, mean_tol=MEAN_TOL):
+    assert tuple(test.shape) == tuple(ref.shape), (what, test.shape, ref.shape)
+    ok, mx, mean = close_16bit(test, ref, max_tol, mean_tol)
+    assert ok, (what, "max", mx, "mean", mean)
+
+
+def grad_tol(name):
+    """Worst-element bound of a gradient by its name (dk, dv, dck, dcv: key/value gradients of an attention operator)."""
+    return KV_GRAD_MAX_TOL if name in ("dk", "dv", "dck", "dcv") else MAX_TOL
+
+
+def rope_tolerance(x, want, ulp, extra=0.0):
+    """Elementwise bound on |rotated - want| where `want` comes from the reference's RotaryEmbedding, which rounds both
+    products x * cos and rotate_half(x) * sin and their sum to the tensor's dtype (module/rope.py:204-209) while the oracle
+    and the kernel round once: half a unit in the last place (`ulp` = 2^-7 for bf16, 2^-10 for fp16: the spacing relative to a value at the bottom of its binade) of each
+    product's operand, of the sum and of the compared result; `extra` adds that many units of the operands."""
+    half = x.shape[-1] // 2
+    mag = x[..., :half].abs() + x[..., half:].abs()
+    mag = torch.cat([mag, mag], -1)
+    return 0.5 * ulp * (mag * (1.0 + 2.0 * extra) + 2.0 * want.abs()) * 1.001 + 1e-6

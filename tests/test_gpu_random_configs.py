@@ -8,6 +8,7 @@ import pytest
 import torch
 
 from oracle import nsa_oracle as O
+from tests.helpers import assert_close_16bit, grad_tol
 
 pytestmark = pytest.mark.gpu
 
@@ -33,20 +34,13 @@ def draw(seed):
 
 
 def fwd_close(t, r, what):
-    """outputs: max |err| <= 2e-2 * max(1, |ref|), mean |err| <= 2e-3"""
-    err = (t.detach().float().cpu() - r.detach().float()).abs()
-    if err.numel():
-        assert float((err / r.detach().abs().clamp(min=1.0)).max()) <= 2e-2 and float(err.mean()) <= 2e-3, what
+    assert_close_16bit(t, r, what)
 
 
 def grad_close(t, r, what):
-    """gradients on their own RMS scale: elementwise <= 0.15 * max(1, |ref| / rms), mean <= 1e-2; a gradient the oracle's
-    autograd leaves undefined (no compressed key anywhere) must be zero here"""
-    r = torch.zeros(t.shape) if r is None else r.float()
-    t = t.float().cpu()
-    rms = float(r.pow(2).mean().sqrt()) or 1.0
-    rel = (t - r).abs() / rms
-    assert float((rel / (r.abs() / rms).clamp(min=1.0)).max()) <= 0.15 and float(rel.mean()) <= 1e-2, what
+    """a gradient the oracle's autograd leaves undefined (no compressed key anywhere) must be zero here"""
+    r = torch.zeros(t.shape) if r is None else r
+    assert_close_16bit(t, r, what, grad_tol(what))
 
 
 @pytest.mark.parametrize("seed", range(24))
@@ -78,13 +72,16 @@ def test_chain_random_configuration(pkg, seed):
     fwd_close(ck, ckr, "ck")
     fwd_close(cv, cvr, "cv")
     assert torch.equal(cu_k.cpu(), cu_kr)
+    # the oracle's attention sees the compressed keys and values the kernels produced (16-bit), so that the selection is
+    # compared on identical scores; its gradients still flow into its own compression (straight-through difference)
+    ckr = ckr + (ck.detach().float().cpu() - ckr).detach()
+    cvr = cvr + (cv.detach().float().cpu() - cvr).detach()
     o1r, idxr, sc = O.compressed_attention(qr, ckr, cvr, ks, st, bs, topk, cu, cu_kr, init_blocks=1, local_blocks=2,
                                            return_scores=True)
     fwd_close(o1, o1r, "o_cmp")
     if idxr is not None:
-        # the oracle scores come from ITS compressed keys (fp32), ours from 16-bit ones: ties within 2e-3
-        bad, differing, rows = O.compare_topk_idx(idx.cpu(), idxr, sc, 2e-3)
-        assert bad <= max(1, rows // 500), (bad, differing, rows)
+        bad, differing, rows = O.compare_topk_idx(idx.cpu(), idxr, sc, 1e-3)
+        assert bad == 0, (bad, differing, rows)
     o2r = O.topk_sparse_attention(qr, kr, vr, idx.cpu(), bs, cu)
     fwd_close(o2, o2r, "o_sel")
     torch.autograd.backward([o1r, o2r], [do1, do2])
