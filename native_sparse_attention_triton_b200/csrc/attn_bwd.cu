@@ -571,6 +571,40 @@ __global__ void convert_rows_kernel(const float* __restrict__ src, void* dst, lo
   *reinterpret_cast<uint2*>(static_cast<T*>(dst) + n * d_sn + (long long)h * d_sh + c * 4) = out;
 }
 
+// (lse, delta) per (token, query head) for the backward passes: delta = sum_d o * dO in fp32.  16 lanes per row of
+// D 16-bit elements (16 bytes each for D = 128); one pass over o and dO.
+template <typename T, int D>
+__global__ void row_stats_kernel(const T* __restrict__ o, const T* __restrict__ dout, const float* __restrict__ lse,
+                                 float2* __restrict__ ld, long long rows, int Hq, long long o_sn, long long o_sh, long long do_sn,
+                                 long long do_sh) {
+  constexpr int EPL = D / 16;  // elements per lane
+  const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+  const int sub = threadIdx.x & 15;
+  float acc = 0.f;
+  if (row < rows) {
+    const long long n = row / Hq;
+    const int h = (int)(row % Hq);
+    const T* po = o + n * o_sn + (long long)h * o_sh + sub * EPL;
+    const T* pd = dout + n * do_sn + (long long)h * do_sh + sub * EPL;
+    if constexpr (EPL == 8) {
+      const uint4 a = *reinterpret_cast<const uint4*>(po), b = *reinterpret_cast<const uint4*>(pd);
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 x = DT<T>::unpack(aw[j]), y = DT<T>::unpack(bw[j]);
+        acc = fmaf(x.x, y.x, acc);
+        acc = fmaf(x.y, y.y, acc);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) acc = fmaf(DT<T>::to_float(po[j]), DT<T>::to_float(pd[j]), acc);
+    }
+  }
+#pragma unroll
+  for (int off = 8; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (row < rows && sub == 0) ld[row] = make_float2(__ldg(lse + row), acc);
+}
+
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 template <typename T, int D, bool SPARSE>
@@ -665,8 +699,11 @@ constexpr int kSparseChunk = 512;  // tokens of one block's list handled by one 
 
 // Token windows of the inverted index: as many tokens as keep the Q and dO rows of one KV-head group (G heads) within
 // about half of the L2 cache, a power of two, at least 1024.  Returns (tokens per window, windows).
+static bool sparse_fused_dq(int G, int D) { return D == 128 && G >= 4 && (G & (G - 1)) == 0; }
+
 static std::pair<int, int> sparse_windows(int N, int G, int D) {
-  const long long bytes_per_token = 2ll * G * D * 2;
+  // Q and dO rows (16-bit) and, where the tcgen05 pass also produces dQ, the fp32 dQ accumulator rows it reduces into
+  const long long bytes_per_token = 2ll * G * D * 2 + (sparse_fused_dq(G, D) ? 4ll * G * D : 0);
   int W = 1024;
   while (2ll * W * bytes_per_token <= (64ll << 20)) W <<= 1;
   return {W, (N + W - 1) / W};
@@ -676,7 +713,8 @@ static size_t sparse_ws_bytes(int N, int batch, int Hq, int Hkv, int D, int topk
   const size_t TB = (size_t)N / block_size + batch;
   const size_t x = (size_t)Hkv * sparse_windows(N, Hq / Hkv, D).second * TB + 1;
   return align_up((size_t)N * Hq * sizeof(float2), 256) + 2 * align_up((size_t)N * Hkv * D * sizeof(float), 256) +
-         4 * align_up(x * sizeof(int), 256) + align_up((size_t)Hkv * N * topk * sizeof(int), 256);
+         4 * align_up(x * sizeof(int), 256) + align_up((size_t)Hkv * N * topk * sizeof(int), 256) +
+         (sparse_fused_dq(Hq / Hkv, D) ? align_up((size_t)N * Hq * D * sizeof(float), 256) : 0);
 }
 
 template <typename T, int D>
@@ -705,9 +743,16 @@ static int run_sparse_bwd(const void* q, const void* k, const void* v, const voi
   int* item_base = reinterpret_cast<int*>(w);
   w += align_up(X * sizeof(int), 256);
   int* list = reinterpret_cast<int*>(w);
+  w += align_up((size_t)Hkv * N * topk * sizeof(int), 256);
+  const bool fused = sparse_fused_dq(G, D);  // dQ comes out of the tcgen05 dK/dV pass; otherwise the per-token dQ kernel runs
+  float* dq32 = fused ? reinterpret_cast<float*>(w) : nullptr;
   // dk32, dv32, count, cursor are contiguous: one memset
   cudaError_t e = cudaMemsetAsync(dk32, 0, reinterpret_cast<uint8_t*>(offsets) - reinterpret_cast<uint8_t*>(dk32), stream);
   if (e != cudaSuccess) return cuda_rc(e);
+  if (fused) {
+    e = cudaMemsetAsync(dq32, 0, (size_t)N * Hq * D * sizeof(float), stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+  }
 
   SparseBwdParams p;
   p.q = q; p.o = o; p.dout = dout; p.lse = lse; p.ld = ld; p.dq = dq; p.topk_idx = topk_idx; p.cu_seqlens = cu;
@@ -729,6 +774,13 @@ static int run_sparse_bwd(const void* q, const void* k, const void* v, const voi
   { LaunchScope ls_("index_scan", stream); index_scan_kernel<<<1, 1024, 0, stream>>>(ip); }
   { LaunchScope ls_("index_fill", stream); index_scatter_kernel<true><<<(unsigned)((hn + 255) / 256), 256, 0, stream>>>(ip); }
   if ((e = cudaGetLastError()) != cudaSuccess) return cuda_rc(e);
+  if (fused) {
+    const long long rows = (long long)N * Hq;
+    LaunchScope ls_("row_stats", stream);
+    row_stats_kernel<T, D><<<(unsigned)((rows * 16 + 255) / 256), 256, 0, stream>>>(
+        static_cast<const T*>(o), static_cast<const T*>(dout), lse, ld, rows, Hq, S[6], S[7], S[8], S[9]);
+    if ((e = cudaGetLastError()) != cudaSuccess) return cuda_rc(e);
+  } else
   {
     // one K buffer and as many warps as shared memory holds: measured 11.7 ms with 6 warps, 10.2 ms with 7, 12.0 ms with
     // 4 warps and two K buffers (64 K tokens) -- the kernel is bound by latency, and warps are what hides it
@@ -749,7 +801,7 @@ static int run_sparse_bwd(const void* q, const void* k, const void* v, const voi
     if ((e = cudaGetLastError()) != cudaSuccess) return cuda_rc(e);
   }
   DkdvParams d;
-  d.ld = ld; d.dk32 = dk32; d.dv32 = dv32; d.cu_q = cu; d.cu_k = cu;
+  d.ld = ld; d.dk32 = dk32; d.dv32 = dv32; d.dq32 = dq32; d.cu_q = cu; d.cu_k = cu;
   d.cu_blocks = cu_blocks; d.offsets = offsets; d.item_base = item_base; d.list = list;
   d.B = batch; d.Hq = Hq; d.Hkv = Hkv; d.G = G; d.TB = TB; d.NW = NW; d.chunk = kSparseChunk; d.block_size = block_size;
   d.window = 1; d.stride = 1; d.causal = 1; d.left = -1;
@@ -766,6 +818,11 @@ static int run_sparse_bwd(const void* q, const void* k, const void* v, const voi
     rc = launch_dkdv<T, D, true>(q, dout, k, v, ds, N, N, grid, d, stream);
   }
   if (rc) return rc;
+  if (fused) {
+    const long long q4 = (long long)N * Hq * (D / 4);
+    LaunchScope ls_("convert_dq", stream);
+    convert_rows_kernel<T><<<(unsigned)((q4 + 255) / 256), 256, 0, stream>>>(dq32, dq, N, Hq, D, S[10], S[11]);
+  }
   const long long n4 = (long long)N * Hkv * (D / 4);
   { LaunchScope ls_("convert_dk", stream); convert_rows_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(dk32, dk, N, Hkv, D, S[12], S[13]); }
   { LaunchScope ls_("convert_dv", stream); convert_rows_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(dv32, dv, N, Hkv, D, S[14], S[15]); }

@@ -11,6 +11,7 @@ struct DkdvParams {
   const float2* ld;    // [Nq, Hq]
   float* dk32;         // [Nk, Hkv, D] fp32 accumulators (zeroed)
   float* dv32;
+  float* dq32 = nullptr;  // sparse tcgen05 pass only: [Nq, Hq, D] fp32 accumulator (zeroed); non-null = also produce dQ
   const int* cu_q;
   const int* cu_k;      // dense: compressed cu; sparse: same as cu_q
   // sparse

@@ -7,9 +7,21 @@
 //     dP   = dO V^T          [128 rows x 64 keys]   A = dO (K-major),  B = V tile (K-major)
 //     dV^T = dO^T P          [128 d    x 64 keys]   A = dO (MN-major), B = P  [rows][keys] (MN-major)
 //     dK^T = Q^T  dS         [128 d    x 64 keys]   A = Q  (MN-major), B = dS [rows][keys] (MN-major)
-// so the token/head rows are the reduction dimension of the last two and the G heads of a KV group are summed
+//     dQ^T = K^T  dS^T       [128 d    x 128 rows]  A = K tile (MN-major), B = dS [rows][keys] (K-major)   (optional)
+// so the token/head rows are the reduction dimension of dV and dK and the G heads of a KV group are summed
 // inside the MMA.  S and dP are double-buffered in TMEM; dV^T and dK^T stay in TMEM for the whole CTA and are added
 // to the fp32 accumulators in global memory at the end.
+//
+// With p.dq32 set the pass also produces dQ: the K tile is already resident and dS already sits in shared memory, so
+// the contribution of this key tile to the rows' dQ costs one more product (4 MMAs of 128 x 128 x 16) and no operand
+// traffic.  A per-token kernel would fetch the 64-key tile again for every token that selected it (32 KB per token and
+// block through the L2-to-SM path, the bound of such a kernel); here the tile is shared by every token of the list and
+// what leaves the SM is the 128 x 128 fp32 partial result, added to the dQ accumulator with red.global.add.f32.  The
+// product is computed TRANSPOSED (d on the TMEM lanes) so that the 32 lanes of a warp hold 32 consecutive d of one
+// (token, head) row: one reduction instruction then covers one whole 128-byte line.  Measured on this part, reductions
+// into L2-resident lines run at 5.2 TB/s when a warp instruction covers whole lines (scalar or v4 alike), 2.8 TB/s when
+// each lane hits its own line (a thread owning a row), and 2.5 TB/s when the lines live in HBM: the work items are
+// ordered by token window (index_scan) so that the accumulator rows being reduced into stay resident in L2.
 //
 // The rows of a tile are scattered tokens (4 KB of Q and of dO each).  One TMA box per token tops out near
 // 26 bytes/clock/SM (the box rate), so the rows are gathered with 16-byte cp.async instead (more than 60
@@ -22,7 +34,13 @@
 //                 dV / dK from TMEM
 //   warps 8..11 : cp.async loaders (warps 8,9: even tiles; 10,11: odd tiles)
 //   warp 12     : TMEM allocation, K/V TMA, MMA issue (converged warp, one elected lane issues)
-// TMEM columns: S0 [0,64) S1 [64,128) dP0 [128,192) dP1 [192,256) dV^T [256,320) dK^T [320,384).
+//   warps 13..16: dQ drain (only with p.dq32): warp w owns the TMEM lanes (= d) of quarter w % 4 and adds the 128 rows of
+//                 every tile's dQ^T to the fp32 accumulator.  They are warps of their own because the reductions are the
+//                 slower of the two streams of this kernel (64 KB per tile at about 19 bytes/clock/SM of L2 reduction
+//                 throughput against 2900 clocks of products): issued from the softmax warps they stalled the P and dS
+//                 phases behind every full reduction queue and the two costs added up (11.6 ms at 64 K tokens instead
+//                 of the 7 ms of the slower stream alone).
+// TMEM columns: S0 [0,64) S1 [64,128) dP0 [128,192) dP1 [192,256) dV^T [256,320) dK^T [320,384) dQ [384,512).
 #include "attn_bwd.h"
 #include "host_util.h"
 #include "tc5.cuh"
@@ -37,7 +55,11 @@ constexpr int kSpRowPanel = 128 * 128;
 constexpr int kSpKvBytes = 64 * 128 * 2;    // K or V tile: 16 KB, 2 panels of [64 keys][64 d]
 constexpr int kSpKvPanel = 64 * 128;
 constexpr int kSpPdBytes = 128 * 64 * 2;    // P or dS tile [128 rows][64 keys]: one panel
-constexpr int kSpThreads = 13 * 32;
+constexpr int kSpThreads = 17 * 32;
+
+__device__ __forceinline__ void red_add1(float* dst, uint32_t v) {
+  asm volatile("red.global.add.f32 [%0], %1;\n" ::"l"(dst), "f"(__uint_as_float(v)) : "memory");
+}
 }  // namespace
 
 template <typename T, int LOGG>
@@ -70,7 +92,10 @@ sparse_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   uint64_t* ds_full = p_empty + 1;
   uint64_t* ds_empty = ds_full + 1;
   uint64_t* all_done = ds_empty + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(all_done + 1);
+  uint64_t* dq_full = all_done + 1;
+  uint64_t* dq_empty = dq_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_empty + 1);
+  const bool with_dq = p.dq32 != nullptr;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int TPT = 128 >> logG;  // tokens per row tile
@@ -124,8 +149,10 @@ sparse_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     mbar_init(p_full, 8);
     mbar_init(p_empty, 1);
     mbar_init(ds_full, 8);
-    mbar_init(ds_empty, 1);
+    mbar_init(ds_empty, with_dq ? 2 : 1);  // dK, and dQ when it is produced, read the dS tile
     mbar_init(all_done, 1);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_empty, 4);
     fence_barrier_init();
   }
   if (warp == 12) {
@@ -227,14 +254,33 @@ sparse_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       }
       __syncwarp();
     };
+    // dQ^T = K^T dS^T: A = K tile MN-major (d as M over two panels, 16 keys = 2048 bytes), B = dS tile K-major (one panel)
+    const uint32_t idesc_q = umma_idesc<T>(128, 128, true, false);
+    auto issue_dq = [&](uint32_t d_tmem) {
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < KT / 16; ++kk)
+          umma_ss(d_tmem, umma_desc_mnmajor(k_addr + kk * 2048, kSpKvPanel), umma_desc_kmajor(ds_addr + kk * 32), idesc_q, kk > 0);
+        umma_commit(dq_full);
+        umma_commit(ds_empty);
+      }
+      __syncwarp();
+    };
     mbar_wait(kv_full, 0, p.st);
-    // Four queues share the tensor pipe: S(i) and dP(i) need their rows and a free TMEM buffer; dV(i) needs P(i) (and
-    // comes after dP(i), so that its completion can release the dO stage); dK(i) needs dS(i).
-    int ns = 0, np = 0, nv = 0, nk = 0;
+    // Five queues share the tensor pipe: S(i) and dP(i) need their rows and a free TMEM buffer; dV(i) needs P(i) (and
+    // comes after dP(i), so that its completion can release the dO stage); dK(i) and dQ(i) need dS(i), dQ(i) also that
+    // dQ(i-1) has been read out of its (single) TMEM buffer.
+    int ns = 0, np = 0, nv = 0, nk = 0, nq = with_dq ? 0 : ntiles;
     long long t0 = 0;
     int idle = 0;
-    while (nk < ntiles) {
+    while (nk < ntiles || nq < ntiles) {
       bool progressed = false;
+      if (nq < np && nq < ntiles && mbar_test(ds_full, nq & 1) && (nq == 0 || mbar_test(dq_empty, (nq - 1) & 1))) {
+        tc_fence_after_sync();
+        issue_dq(tmem + 384);
+        ++nq;
+        progressed = true;
+      }
       if (nv < np && mbar_test(p_full, nv & 1)) {
         tc_fence_after_sync();
         issue_grad(do_base + (nv % kSpDoStages) * kSpRowBytes, p_addr, tmem + 256, nv == 0, do_empty + (nv % kSpDoStages), p_empty);
@@ -248,7 +294,7 @@ sparse_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         ++ns;
         progressed = true;
       }
-      if (nk < np && mbar_test(ds_full, nk & 1)) {
+      if (nk < np && nk < ntiles && mbar_test(ds_full, nk & 1)) {
         tc_fence_after_sync();
         issue_grad(q_base + (nk % kSpQStages) * kSpRowBytes, ds_addr, tmem + 320, nk == 0, q_empty + (nk % kSpQStages), ds_empty);
         ++nk;
@@ -275,6 +321,45 @@ sparse_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     }
     if (elect_one()) umma_commit(all_done);
     __syncwarp();
+  } else if (warp >= 13) {
+    // ===================== dQ drain: lane = d, 128 columns = the rows of the tile =====================
+    if (with_dq) {
+      constexpr int SPC = 32 >> LOGG;  // tokens (slots) per chunk of 32 columns
+      const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16) + 384;
+      float* const dst = p.dq32 + (long long)(h * G) * D + (warp & 3) * 32 + lane;
+      // one reduction per row: the warp's 32 lanes add 32 consecutive floats of the (token, head) row
+      auto reduce_chunk = [&](const uint32_t (&r)[32], int i, int c) {
+#pragma unroll
+        for (int s2 = 0; s2 < SPC; ++s2) {
+          const int ti = i * TPT + c * SPC + s2;
+          const int n = ti < tok_count ? __ldg(p.list + tok_begin + ti) : -1;
+          if (n >= 0) {
+            float* row_dst = dst + (long long)n * p.Hq * D;
+#pragma unroll
+            for (int g = 0; g < G; ++g) red_add1(row_dst + g * D, r[s2 * G + g]);
+          }
+        }
+      };
+      for (int i = 0; i < ntiles; ++i) {
+        mbar_wait(dq_full, i & 1, p.st);
+        tc_fence_after_sync();
+        uint32_t ra[32], rb[32];
+        tmem_ld32(lane_base, ra);
+        tmem_ld32(lane_base + 32, rb);
+        tmem_ld_wait();
+        reduce_chunk(ra, i, 0);
+        reduce_chunk(rb, i, 1);
+        tmem_ld32(lane_base + 64, ra);
+        tmem_ld32(lane_base + 96, rb);
+        tmem_ld_wait();
+        // the rest of the buffer is in registers: the next tile's product may overwrite it
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dq_empty);
+        reduce_chunk(ra, i, 2);
+        reduce_chunk(rb, i, 3);
+      }
+    }
   } else {
     // ===================== softmax / dS threads: two threads per row (32 of the 64 key columns each) =====================
     const int half = warp >> 2;

@@ -144,7 +144,10 @@ def box_fixture(name):
 # score up to 0.128 there against the fp32 oracle and these kernels 0.074 (BASELINE configurations 1 and 2, measured on a
 # B200 by tests/test_gpu_vs_reference.py); every other tensor of either implementation stayed below 1.5e-2, means below
 # 1.7e-3.
-MAX_TOL, MEAN_TOL, KV_GRAD_MAX_TOL = 2e-2, 2e-3, 8e-2
+# Gradients that pass through two operators' backward passes in a row (attention, then compression: dk, dv, dwk, dwv of
+# the chain) carry both operators' rounding; their mean bound is CHAIN_GRAD_MEAN_TOL.  The reference's own recorded chain
+# (tests/golden/box_triton_*.npz) scores 2.3e-3 .. 2.8e-3 there against the fp32 oracle, these kernels 2.0e-3 .. 2.8e-3.
+MAX_TOL, MEAN_TOL, KV_GRAD_MAX_TOL, CHAIN_GRAD_MEAN_TOL = 2e-2, 2e-3, 8e-2, 4e-3
 
 
 def error_16bit(test, ref):

@@ -62,6 +62,6 @@ def test_layer_forward_backward(Hq, Hkv, seqlens, topk, window):
     # three branch outputs, each within the operator tolerance (2e-2 / 2e-3), computed from 16-bit rotated inputs and summed
     assert float((err / y2.detach().abs().clamp(min=1.0)).max()) <= 4e-2 and float(err.mean()) <= 3e-3
     for n in names:
-        close(t[n].grad, r[n].grad, "d" + n)
-    close(gate_g.grad, gate_r.grad, "dgate")
+        close(t[n].grad, r[n].grad, "d" + n, chain=True)
+    close(gate_g.grad, gate_r.grad, "dgate", chain=True)
     assert status_ok()
