@@ -1,5 +1,6 @@
 """Helpers shared by the operator wrappers: argument plumbing between torch tensors and the C ABI."""
 import math
+import weakref
 from typing import List
 
 import torch
@@ -35,9 +36,25 @@ def inner_contiguous(t: torch.Tensor) -> torch.Tensor:
     return t if ok else t.contiguous()
 
 
+_host_seqlens_cache = {}   # id(tensor) -> (weak reference, tensor version, list)
+
+
 def host_seqlens(cu_seqlens: torch.Tensor) -> List[int]:
-    """cu_seqlens -> python list (one device-to-host copy)."""
-    return cu_seqlens.tolist()
+    """cu_seqlens -> python list.  Costs one device-to-host copy (a synchronisation) the first time a tensor object is
+    seen; the result is remembered for as long as that same object lives and is not written to (its version counter),
+    so a training loop that passes the same cu_seqlens tensor every step does not synchronise every step."""
+    key = id(cu_seqlens)
+    hit = _host_seqlens_cache.get(key)
+    if hit is not None and hit[0]() is cu_seqlens and hit[1] == cu_seqlens._version:
+        return hit[2]
+    out = cu_seqlens.tolist()
+    if len(_host_seqlens_cache) > 64:
+        for k in [k for k, v in _host_seqlens_cache.items() if v[0]() is None]:
+            del _host_seqlens_cache[k]
+        if len(_host_seqlens_cache) > 64:
+            _host_seqlens_cache.clear()
+    _host_seqlens_cache[key] = (weakref.ref(cu_seqlens), cu_seqlens._version, out)
+    return out
 
 
 def compressed_lens(cu: List[int], kernel_size: int, kernel_stride: int) -> List[int]:

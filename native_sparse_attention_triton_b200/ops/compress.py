@@ -17,6 +17,25 @@ from ._common import (compressed_lens, cumsum_tensor, dtype_code, host_seqlens, 
 _KERNEL_SIZES = {16, 32, 64, 128}
 
 
+_layout_cache = {}   # (id(cu_seqlens), kernel_size, kernel_stride) -> (host list it was derived from, y_lens, y_cu, y_cu version)
+
+
+def _compressed_layout(cu_seqlens, cu, kernel_size, kernel_stride, device):
+    """(compressed lengths, their device prefix sum) for a cu_seqlens tensor; remembered per (tensor object, kernel) so
+    that repeated calls with the same tensor upload nothing.  `cu` is the host copy host_seqlens returned for it: the
+    entry is valid only while that very list is still the cached copy (same object, not written to since)."""
+    key = (id(cu_seqlens), kernel_size, kernel_stride)
+    hit = _layout_cache.get(key)
+    if hit is not None and hit[0] is cu and hit[2]._version == hit[3] and hit[2].device == device:
+        return hit[1], hit[2]
+    y_lens = compressed_lens(cu, kernel_size, kernel_stride)
+    y_cu = cumsum_tensor(y_lens, device)
+    if len(_layout_cache) > 64:
+        _layout_cache.clear()
+    _layout_cache[key] = (cu, y_lens, y_cu, y_cu._version)
+    return y_lens, y_cu
+
+
 class _Compress(torch.autograd.Function):
     """mode: 'linear' | 'weighted' | 'avg'."""
 
@@ -27,8 +46,7 @@ class _Compress(torch.autograd.Function):
         x = inner_contiguous(x)
         cu = host_seqlens(cu_seqlens)
         batch = len(cu) - 1
-        y_lens = compressed_lens(cu, kernel_size, kernel_stride)
-        y_cu = cumsum_tensor(y_lens, x.device)
+        y_lens, y_cu = _compressed_layout(cu_seqlens, cu, kernel_size, kernel_stride, x.device)
         total_y, max_y = sum(y_lens), max(y_lens) if y_lens else 0
         y = torch.empty(total_y, num_heads, head_dim, dtype=x.dtype, device=x.device)
         bias = torch.empty(num_heads, head_dim, dtype=x.dtype, device=x.device) if pe is not None else None

@@ -172,9 +172,13 @@ def assert_close_16bit(test, ref, what, max_tol=MAX_TOL, mean_tol=MEAN_TOL):
     assert ok, (what, "max", mx, "mean", mean)
 
 
-def grad_tol(name):
-    """Worst-element bound of a gradient by its name (dk, dv, dck, dcv: key/value gradients of an attention operator)."""
-    return KV_GRAD_MAX_TOL if name in ("dk", "dv", "dck", "dcv") else MAX_TOL
+def grad_tol(name, chain=False):
+    """Worst-element bound of a gradient by its name: dk, dv, dck, dcv are key/value gradients of an attention operator;
+    in a chain of operators the compression weights' gradients (dwk, dwv) are sums of those over windows and inherit half
+    of their allowance (the reference's recorded chain reaches 2.3e-2 there against the fp32 oracle)."""
+    if name in ("dk", "dv", "dck", "dcv"):
+        return KV_GRAD_MAX_TOL
+    return KV_GRAD_MAX_TOL / 2 if chain and name in ("dwk", "dwv") else MAX_TOL
 
 
 def rope_tolerance(x, want, ulp, extra=0.0):

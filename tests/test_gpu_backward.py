@@ -24,7 +24,7 @@ def status_ok():
 def close(test, ref, what, chain=False):
     """The acceptance rule of tests/helpers.py; key/value gradients of the attention operators get their own worst-element
     bound, gradients of a chain of operators (chain=True) their own mean bound."""
-    assert_close_16bit(test, ref, what, grad_tol(what), CHAIN_GRAD_MEAN_TOL if chain else MEAN_TOL)
+    assert_close_16bit(test, ref, what, grad_tol(what, chain), CHAIN_GRAD_MEAN_TOL if chain else MEAN_TOL)
 
 
 def leaf(t, dtype=torch.bfloat16):

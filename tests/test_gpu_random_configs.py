@@ -40,7 +40,7 @@ def fwd_close(t, r, what):
 def grad_close(t, r, what):
     """a gradient the oracle's autograd leaves undefined (no compressed key anywhere) must be zero here"""
     r = torch.zeros(t.shape) if r is None else r
-    assert_close_16bit(t, r, what, grad_tol(what), CHAIN_GRAD_MEAN_TOL)
+    assert_close_16bit(t, r, what, grad_tol(what, chain=True), CHAIN_GRAD_MEAN_TOL)
 
 
 @pytest.mark.parametrize("seed", range(24))

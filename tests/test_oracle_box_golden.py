@@ -58,7 +58,7 @@ def test_oracle_matches_reference_triton_chain(name):
     for a, b in checks:
         # the fixture holds the reference's 16-bit kernels: its key/value gradients carry up to 0.128 of worst-element
         # error against this oracle (tests/helpers.py), everything else stays inside the common rule
-        ok, mx, mean = close_16bit(a, from_bits(z[b]), 0.16 if grad_tol(b) > 2e-2 else (4e-2 if b.startswith("dw") else 2e-2),
+        ok, mx, mean = close_16bit(a, from_bits(z[b]), 2 * grad_tol(b, chain=True) if b.startswith("d") and b != "dq" else 2e-2,
                                    REF_GRAD_MEAN_TOL if b.startswith("d") else 2e-3)
         print(name, b, "max", mx, "mean", mean)
         assert ok, (b, mx, mean)
