@@ -62,6 +62,26 @@ class RotaryEmbedding:
         return ys
 
 
+def _device_rope_of(rope):
+    """A RotaryEmbedding of this module with the frequencies of a foreign rotary-embedding object (the reference's
+    module/rope.py:RotaryEmbedding exposes ``inv_freq`` and ``attention_scaling``), made once and kept on that object; None
+    when the object has no fixed frequencies (dynamic rope types recompute them from the sequence length).  It lets a decode
+    step driven by the reference's own layer read its positions from the cache counters on the device instead of from the
+    host-side step number, which is what makes the step free of host synchronisation."""
+    mine = getattr(rope, "_nsa_b200_rope", None)
+    if mine is not None:
+        return mine
+    inv_freq, scaling = getattr(rope, "inv_freq", None), getattr(rope, "attention_scaling", None)
+    if not torch.is_tensor(inv_freq) or scaling is None or "dynamic" in str(getattr(rope, "rope_type", "")):
+        return None
+    mine = RotaryEmbedding(inv_freq.detach().float().contiguous(), float(scaling))
+    try:
+        object.__setattr__(rope, "_nsa_b200_rope", mine)
+    except Exception:
+        pass
+    return mine
+
+
 def _compress_staged(cache: NSACache, batch: int, which: int, func: Callable, weight, pe):
     """One compressed row per sequence from the staging buffers [batch * kernel_size, heads, d] (the reference runs its
     compress function over them with an arange cu_seqlens, infer/inference_func.py:56-87).  The library's own compress
@@ -125,10 +145,11 @@ def nsa_infer(cu_seqlens: torch.Tensor, step: int, query: torch.Tensor, key: tor
     cache.prepare_compress(cu_seqlens, step, key, value)
     compress_key = _compress_staged(cache, batch, 0, compress_func[0], compress_weight[0], intra_block_pe)
     compress_value = _compress_staged(cache, batch, 1, compress_func[1], compress_weight[1], None)
-    if hasattr(rope, "decode_at3"):
+    fast_rope = rope if hasattr(rope, "decode_at3") else _device_rope_of(rope)
+    if fast_rope is not None:
         # the new token's index is the number of tokens cached so far; the compressed token's, the compressed count
-        query, key, compress_key = rope.decode_at3(query, key, compress_key, cache.sparse_kv_len, cache.compress_kv_len,
-                                                    kernel_stride)
+        query, key, compress_key = fast_rope.decode_at3(query, key, compress_key, cache.sparse_kv_len, cache.compress_kv_len,
+                                                         kernel_stride)
     else:
         compress_cu = torch.zeros(batch + 1, dtype=torch.int32, device=key.device)
         compress_cu[1:] = torch.cumsum(cache.compress_kv_len[:batch], 0)
