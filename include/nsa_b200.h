@@ -100,9 +100,18 @@ int nsa_pool_compress_fwd(const void* x, const void* w, const void* pe, const in
                           int num_heads, int head_dim, int kernel_size, int kernel_stride,
                           long long x_stride_n, long long x_stride_h, int dtype, void* stream);
 
-/* Number of split-KV partitions the decode kernels want for this problem (>= 1); the caller sizes
- * the scratch buffer as batch*num_kv_heads*splits*16*(head_dim+2) floats.  No counterpart in the reference. */
+/* Number of split-KV partitions the decode kernels want for this problem (>= 1; max_tiles = 64-key tiles of the longest
+ * row a pair can have), and the floats of scratch a call with that many splits needs: control words (a task counter and a
+ * per-(sequence, KV head) counter at the FRONT of the scratch: batch*num_kv_heads + 1 ints), the splits' partial results
+ * and, for the compressed operator, the logits of every compressed key (cache_len keys per pair).  The control words must
+ * be ZERO before the first call that uses a scratch buffer; every completed call leaves them zero again (they count with
+ * wrap-around), so a buffer cleared once can be reused by any sequence of calls that do not overlap on the GPU -- except
+ * that a call with MORE pairs than the previous call on the same buffer must clear its (longer) control region again,
+ * because the previous call's partial results start right behind the shorter one.  One split of the flash / top-k
+ * operators needs no scratch.  No counterpart in the reference. */
 int nsa_decode_num_splits(int batch, int num_kv_heads, int max_tiles);
+long long nsa_decode_scratch_floats(int batch, int num_kv_heads, int head_dim, int num_splits);
+long long nsa_compressed_decode_scratch_floats(int batch, int num_kv_heads, int head_dim, int num_splits, int cache_len);
 
 /* Single-token attention over the first seqlens[b] rows of a dense cache.
  * Replaces decode_kernel, native_sparse_attention/ops/triton/flash_attention_decode.py:22-217.
@@ -118,16 +127,16 @@ int nsa_flash_attn_decode(const void* q, const void* k, const void* v, const int
  * allocation can imply).  It has no counterpart in the reference.  The split-KV scratch is an 8 MiB array
  * inside the library's device image (held by every GPU that loads the library, until the process exits);
  * the caller passes inputs and the output only.  No cudaMalloc/cudaFree or allocating routine is called.
- *   num_splits: 0 = the library chooses (nsa_decode_num_splits, lowered until the partial results fit the array, so
+ *   num_splits: 0 = the library chooses (nsa_decode_num_splits, lowered until the scratch fits the array, so
  *       this never fails for size); > 0 = that many (at most 64, at most one per 64-key tile): the call then needs
- *       batch*num_kv_heads*splits*16*(head_dim+2) floats and returns -3 when that exceeds
+ *       nsa_decode_scratch_floats(batch, num_kv_heads, head_dim, splits) floats and returns -3 when that exceeds
  *       nsa_flash_attn_decode_static_capacity() floats -- ask for fewer splits (1 needs none).
  *   The first call on a device may come from any host thread (the address lookup is serialised).
  *   The first call on a device looks up the array's device address (cudaGetSymbolAddress, once per device,
  *   with that device current): make that first call before any stream capture.
- *   All calls on a device share the one array and it keeps the previous call's contents; nothing has to be
- *   cleared (each call writes every slot it later reads), but two calls that overlap on the GPU (different
- *   streams, or host threads) race on it: serialise them. */
+ *   All calls on a device share the one array and it keeps the previous call's contents; its control words start at
+ *   zero and every completed call returns them to zero, every other slot is written before it is read, so the caller
+ *   clears nothing, but two calls that overlap on the GPU (different streams, or host threads) race on it: serialise them. */
 long long nsa_flash_attn_decode_static_capacity(void);
 int nsa_flash_attn_decode_static(const void* q, const void* k, const void* v, const int* seqlens, void* o,
                                  int num_splits, int batch, int cache_len, int num_q_heads, int num_kv_heads,
@@ -142,16 +151,20 @@ int nsa_topk_sparse_attn_decode(const void* q, const void* k, const void* v, con
                                 int head_dim, int topk, int block_size, const long long* strides,
                                 float sm_scale, int dtype, void* stream);
 
-/* Single-token attention over the compressed cache + block scores + top-k selection in one kernel.
+/* Single-token attention over the compressed cache + block scores + top-k selection in one kernel (split-KV; the warp
+ * that finishes a (sequence, KV head) pair merges the partial results, scores the blocks and selects).
  * Replaces compressed_attention_decode (about 15 ATen launches),
  * native_sparse_attention/ops/torch/compressed_attention_decode.py:21-153.
- *   topk_idx int32 [Hkv, B, min(topk, ceil(max_seqlen/block_size))] or NULL (output only). */
+ *   topk_idx int32 [Hkv, B, min(topk, ceil(max_seqlen/block_size))] or NULL (output only).
+ *   scratch: nsa_compressed_decode_scratch_floats(batch, num_kv_heads, head_dim, num_splits, cache_len) floats, always
+ *   needed (-3 otherwise).  -2 when cache_len + ceil(max_seqlen/block_size) floats exceed two key tiles (about 8000 at
+ *   head_dim 128: contexts beyond ~100 K tokens at stride 16). */
 int nsa_compressed_attn_decode(const void* q, const void* k, const void* v, const int* seqlens,
-                               const int* compress_seqlens, void* o, int* topk_idx, int batch, int cache_len,
-                               int max_seqlen, int num_q_heads, int num_kv_heads, int head_dim,
-                               int kernel_size, int kernel_stride, int block_size, int topk, int init_blocks,
-                               int local_blocks, const long long* strides, float sm_scale, int dtype,
-                               void* stream);
+                               const int* compress_seqlens, void* o, int* topk_idx, float* scratch,
+                               long long scratch_floats, int num_splits, int batch, int cache_len, int max_seqlen,
+                               int num_q_heads, int num_kv_heads, int head_dim, int kernel_size, int kernel_stride,
+                               int block_size, int topk, int init_blocks, int local_blocks, const long long* strides,
+                               float sm_scale, int dtype, void* stream);
 
 /* Bytes of scratch nsa_varlen_attn_bwd needs.  No counterpart in the reference (it allocates
  * [G, total_k, Hkv, d] per-head buffers inside _compressed_attention_bwd, compressed_attention.py:664-669). */

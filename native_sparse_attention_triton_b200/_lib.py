@@ -46,8 +46,8 @@ _SIGNATURES = {
     "nsa_flash_attn_decode": [_P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P, _F, _I, _P],
     "nsa_flash_attn_decode_static": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _F, _I, _P],
     "nsa_topk_sparse_attn_decode": [_P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _P, _F, _I, _P],
-    "nsa_compressed_attn_decode": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P,
-                                   _F, _I, _P],
+    "nsa_compressed_attn_decode": [_P, _P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I,
+                                   _I, _P, _F, _I, _P],
 }
 
 
@@ -57,6 +57,8 @@ _SIZE_QUERIES = {
     "nsa_topk_sparse_attn_bwd_workspace": [_I, _I, _I, _I, _I, _I, _I],
     "nsa_launch_count": [],
     "nsa_flash_attn_decode_static_capacity": [],
+    "nsa_decode_scratch_floats": [_I, _I, _I, _I],
+    "nsa_compressed_decode_scratch_floats": [_I, _I, _I, _I, _I],
 }
 
 

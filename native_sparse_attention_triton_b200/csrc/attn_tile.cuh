@@ -146,13 +146,18 @@ __device__ __forceinline__ void online_softmax_step(float (&s)[8][4], const int 
 //   tile_at(i, kpos, lim) : position token of tile i and its number of leading visible keys
 //   issue(is_v, kpos)     : lane 0 starts the TMA load of that tile into kbuf / vbuf (with expect_tx)
 // barK / barV are single-arrival mbarriers owned by the warp; `phase` carries their parity.
-template <typename T, int D, typename TileAt, typename Issue>
+// on_scores(kpos, limv, s) sees every tile's raw logits (mma accumulator layout, before scaling and masking).
+struct NoScoreHook {
+  __device__ __forceinline__ void operator()(int, int, const float (&)[8][4]) const {}
+};
+template <typename T, int D, typename TileAt, typename Issue, typename OnScores = NoScoreHook>
 __device__ __forceinline__ void warp_attend_tiles(const uint32_t (&qf)[D / 16][4], float (&o)[D / 8][4], float (&m)[2],
                                                   float (&l)[2], int ntiles, uint32_t kbuf, uint32_t vbuf, uint64_t* barK,
                                                   uint64_t* barV, uint32_t& phase, float scale2, const Status& st,
-                                                  TileAt tile_at, Issue issue) {
+                                                  TileAt tile_at, Issue issue, OnScores on_scores = OnScores(),
+                                                  bool first_tile_issued = false) {
   const int lane = lane_id();
-  if (ntiles > 0 && lane == 0) {
+  if (ntiles > 0 && lane == 0 && !first_tile_issued) {
     int kpos, limv;
     tile_at(0, kpos, limv);
     issue(false, kpos);
@@ -169,6 +174,7 @@ __device__ __forceinline__ void warp_attend_tiles(const uint32_t (&qf)[D / 16][4
     mma_nk<T, 8, D / 16, kKeyTile>(s, qf, kbuf, 0, 0);
     __syncwarp();
     if (i + 1 < ntiles && lane == 0) issue(false, knext);
+    on_scores(kpos, limv, s);
     const int lim[2] = {limv, limv};
     online_softmax_step<D / 8>(s, lim, scale2, m, l, o);
     uint32_t pf[4][4];

@@ -186,15 +186,25 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(PoolFwdParams p) {
   const T* x = static_cast<const T*>(p.x) + (long long)(__ldg(p.cu + b) + m * p.stride) * p.x_sn + (long long)h * p.x_sh + c * 8;
   const T* w = p.w ? static_cast<const T*>(p.w) + h * p.ks : nullptr;
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  for (int k = 0; k < p.ks; ++k) {
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + (long long)k * p.x_sn));
-    const float wv = w ? DT<T>::to_float(w[k]) : 1.f;
-    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+  // eight taps per step (kernel sizes are multiples of 16): eight independent 16-byte loads in flight per thread, which
+  // is what keeps HBM busy on long inputs and keeps the chain of dependent loads short on the few rows of a decode step
+  for (int k0 = 0; k0 < p.ks; k0 += 8) {
+    uint4 v[8];
+    float wv[8];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float2 f = DT<T>::unpack(u[e]);
-      acc[2 * e] += wv * f.x;
-      acc[2 * e + 1] += wv * f.y;
+    for (int u = 0; u < 8; ++u) {
+      v[u] = __ldg(reinterpret_cast<const uint4*>(x + (long long)(k0 + u) * p.x_sn));
+      wv[u] = w ? DT<T>::to_float(w[k0 + u]) : 1.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const uint32_t uu[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = DT<T>::unpack(uu[e]);
+        acc[2 * e] += wv[u] * f.x;
+        acc[2 * e + 1] += wv[u] * f.y;
+      }
     }
   }
   if (!w) {

@@ -187,7 +187,7 @@ class DecodeGraph:
             nsa_infer(cu_seqlens, 1, *self.inputs, **self.args)
         torch.cuda.current_stream(query.device).wait_stream(side)
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        with torch.cuda.graph(self.graph, stream=side):   # the warm-up stream: its decode scratch is reused by the capture
             self.output = nsa_infer(cu_seqlens, 1, *self.inputs, **self.args)
         for dst, src in zip(self._state(cache), state):
             dst.copy_(src)

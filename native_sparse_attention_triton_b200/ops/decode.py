@@ -20,12 +20,49 @@ def _decode_strides(q, k, v, o, topk_idx=None):
                               v.stride(2), o.stride(0), o.stride(1), *t)
 
 
-def _scratch(batch, num_kv_heads, head_dim, max_tiles, device):
-    splits = _lib.lib().nsa_decode_num_splits(batch, num_kv_heads, max_tiles)
-    if splits <= 1:
-        return 1, None, 0
-    n = batch * num_kv_heads * splits * 16 * (head_dim + 2)
-    return splits, torch.empty(n, dtype=torch.float32, device=device), n
+_scratch_cache = {}   # (device index, stream handle) -> float32 tensor whose control words are zero between calls
+
+
+def _scratch(batch, num_kv_heads, head_dim, max_tiles, device, compressed_cache_len=None):
+    """(splits, scratch tensor or None, its size in floats) for one decode call: the split count the library asks for and
+    the scratch that count needs (control words, partial results, and the logits of the compressed operator).
+
+    The kernels leave the control words at zero when they finish, so a buffer zeroed once serves every later call that is
+    ordered after it: one buffer is kept per (device, stream) -- calls on one stream cannot overlap -- and regrown (and
+    zeroed again) when a call needs more.  A CUDA-graph capture uses the buffer of its capture stream when a warm-up call on
+    that stream has made one (DecodeGraph does), else a fresh zeroed buffer from the graph's pool."""
+    lib = _lib.lib()
+    splits = lib.nsa_decode_num_splits(batch, num_kv_heads, max_tiles)
+    if compressed_cache_len is None:
+        n = lib.nsa_decode_scratch_floats(batch, num_kv_heads, head_dim, splits)
+    else:
+        n = lib.nsa_compressed_decode_scratch_floats(batch, num_kv_heads, head_dim, splits, compressed_cache_len)
+    if n <= 0:
+        return splits, None, 0
+    ctrl = (batch * num_kv_heads + 1 + 63) // 64 * 64
+
+    def fresh(size):
+        buf = torch.empty(size, dtype=torch.float32, device=device)
+        buf[:ctrl].zero_()
+        return buf
+
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream_ptr(device))
+    buf = _scratch_cache.get(key)
+    if torch.cuda.is_current_stream_capturing() and (buf is None or buf.numel() < n or buf._nsa_ctrl < ctrl):
+        return splits, fresh(n), n   # from the graph's own pool, zeroed by a captured kernel at every replay
+    if buf is None or buf.numel() < n:
+        buf = fresh(max(n, 0 if buf is None else buf.numel()))
+        _scratch_cache[key] = buf
+    elif buf._nsa_ctrl < ctrl:
+        # the control region grows with batch * kv_heads; beyond the previous call's region lie that call's partial results
+        buf[:ctrl].zero_()
+    buf._nsa_ctrl = ctrl
+    return splits, buf, n
+
+
+def _drop_scratch(device):
+    """Forget the stream's scratch after a failed call: its control words may not have returned to zero."""
+    _scratch_cache.pop((device.index if device.index is not None else torch.cuda.current_device(), stream_ptr(device)), None)
 
 
 def _check_decode(q, k, v, seqlens):
@@ -58,6 +95,8 @@ def flash_attention_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, se
     rc = _lib.lib().nsa_flash_attn_decode(ptr(q), ptr(k), ptr(v), ptr(seqlens), ptr(o), ptr(scratch), n, splits, batch,
                                           cache_len, num_q_heads, num_kv_heads, head_dim, _decode_strides(q, k, v, o),
                                           float(sm_scale), dtype_code(q), stream_ptr(q.device))
+    if rc:
+        _drop_scratch(q.device)
     _lib.check(rc, "nsa_flash_attn_decode")
     return o
 
@@ -87,6 +126,8 @@ def topk_sparse_attention_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tens
                                                 ptr(scratch), n, splits, batch, cache_len, num_q_heads, num_kv_heads,
                                                 head_dim, topk, int(block_size), _decode_strides(q, k, v, o, topk_idx),
                                                 float(sm_scale), dtype_code(q), stream_ptr(q.device))
+    if rc:
+        _drop_scratch(q.device)
     _lib.check(rc, "nsa_topk_sparse_attn_decode")
     return o
 
@@ -120,11 +161,14 @@ def compressed_attention_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
     t_out = min(topk, max_blocks)
     o = torch.empty_like(q)
     topk_idx = torch.empty(num_kv_heads, batch, t_out, dtype=torch.int32, device=q.device)
+    splits, scratch, n = _scratch(batch, num_kv_heads, head_dim, (cache_len + 63) // 64, q.device, cache_len)
     torch.cuda.set_device(q.device)
     rc = _lib.lib().nsa_compressed_attn_decode(ptr(q), ptr(k), ptr(v), ptr(seqlens), ptr(compress_seqlens), ptr(o),
-                                               ptr(topk_idx), batch, cache_len, max_seqlen, num_q_heads, num_kv_heads,
-                                               head_dim, kernel_size, kernel_stride, block_size, topk, init_blocks,
-                                               local_blocks, _decode_strides(q, k, v, o, topk_idx), float(sm_scale),
-                                               dtype_code(q), stream_ptr(q.device))
+                                               ptr(topk_idx), ptr(scratch), n, splits, batch, cache_len, max_seqlen,
+                                               num_q_heads, num_kv_heads, head_dim, kernel_size, kernel_stride, block_size,
+                                               topk, init_blocks, local_blocks, _decode_strides(q, k, v, o, topk_idx),
+                                               float(sm_scale), dtype_code(q), stream_ptr(q.device))
+    if rc:
+        _drop_scratch(q.device)
     _lib.check(rc, "nsa_compressed_attn_decode")
     return o, topk_idx
