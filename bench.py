@@ -369,6 +369,44 @@ def decode_step_microbench(dev):
                 status=pkg.device_status())
 
 
+def decode_inputs(dev, B, L, Hq, Hkv, T, ragged):
+    """Seeded inputs of a decode case: caches [B, L, Hkv, 128], one query row per sequence, lengths, a random selection of
+    T blocks per (head, sequence) and the compressed caches (kernel 32, stride 16)."""
+    g = torch.Generator().manual_seed(42)
+    d, bs, ks, st = 128, 64, 32, 16
+    if ragged:
+        seqlens = torch.clamp(torch.arange(B, dtype=torch.int32) % 76 * 128 + 1, max=L)
+        seqlens = seqlens[torch.randperm(B, generator=g)]
+    else:
+        seqlens = torch.full((B,), 8192 + 64, dtype=torch.int32)
+    q = torch.randn(B, Hq, d, generator=g).to(torch.bfloat16).to(dev)
+    k = torch.randn(B, L, Hkv, d, dtype=torch.bfloat16, device=dev)
+    v = torch.randn(B, L, Hkv, d, dtype=torch.bfloat16, device=dev)
+    Lc = (L - ks) // st + 1
+    ck, cv = k[:, :Lc].contiguous(), v[:, :Lc].contiguous()
+    clen = torch.clamp((seqlens - ks) // st + 1, min=0).to(torch.int32)
+    nb = (seqlens.long() - 1) // bs + 1
+    idx = torch.full((Hkv, B, T), -1, dtype=torch.int32)
+    for b in range(B):
+        n = int(nb[b])
+        for h in range(Hkv):
+            pick = torch.randperm(n, generator=g)[: min(T, n)].sort().values
+            idx[h, b, : pick.numel()] = pick.int()
+    return dict(q=q, k=k, v=v, ck=ck, cv=cv, seqlens=seqlens, clen=clen, idx=idx.to(dev), sl=seqlens.to(dev), cl=clen.to(dev),
+                d=d, bs=bs, ks=ks, st=st, T=T)
+
+
+def decode_profile_case(ops, dev):
+    """Two rounds of (flash, selected-block, compressed) decode on the bandwidth case: launches 3..5 are the warm ones."""
+    x = decode_inputs(dev, 76, 8192, 32, 4, 16, True)
+    for _ in range(2):
+        ops.flash_attention_decode(x["q"], x["k"], x["v"], x["sl"])
+        ops.topk_sparse_attention_decode(x["q"], x["k"], x["v"], x["idx"], x["bs"], x["sl"])
+        ops.compressed_attention_decode(x["q"], x["ck"], x["cv"], x["sl"], x["cl"], x["ks"], x["st"], x["bs"], x["T"], max_seqlen=8192)
+    torch.cuda.synchronize()
+    print(json.dumps(dict(decode_profile="ok")))
+
+
 def decode_microbench(ops, dev):
     """The three single-token operators on (a) the bandwidth-sized case of the reference's decode self-tests
     (batch 76, cache 8192, 32q/4kv heads, d=128, block 64, top-16, ragged lengths), (b) the same case with four times
@@ -379,28 +417,10 @@ def decode_microbench(ops, dev):
     out = {}
     for tag, B, L, Hq, Hkv in (("bandwidth_case", 76, 8192, 32, 4), ("bandwidth_case_batch_304", 304, 8192, 32, 4),
                                ("generation_case", 4, 8192 + 128, 32, 2)):
-        g = torch.Generator().manual_seed(42)
-        d, bs, T, ks, st = 128, 64, 16 if tag.startswith("bandwidth_case") else 8, 32, 16
-        if tag.startswith("bandwidth_case"):
-            seqlens = torch.clamp(torch.arange(B, dtype=torch.int32) % 76 * 128 + 1, max=L)
-            seqlens = seqlens[torch.randperm(B, generator=g)]
-        else:
-            seqlens = torch.full((B,), 8192 + 64, dtype=torch.int32)
-        q = torch.randn(B, Hq, d, generator=g).to(torch.bfloat16).to(dev)
-        k = torch.randn(B, L, Hkv, d, dtype=torch.bfloat16, device=dev)
-        v = torch.randn(B, L, Hkv, d, dtype=torch.bfloat16, device=dev)
-        Lc = (L - ks) // st + 1
-        ck, cv = k[:, :Lc].contiguous(), v[:, :Lc].contiguous()
-        clen = torch.clamp((seqlens - ks) // st + 1, min=0).to(torch.int32)
-        sl, cl = seqlens.to(dev), clen.to(dev)
-        nb = (seqlens.long() - 1) // bs + 1
-        idx = torch.full((Hkv, B, T), -1, dtype=torch.int32)
-        for b in range(B):
-            n = int(nb[b])
-            for h in range(Hkv):
-                pick = torch.randperm(n, generator=g)[: min(T, n)].sort().values
-                idx[h, b, : pick.numel()] = pick.int()
-        idx = idx.to(dev)
+        T = 16 if tag.startswith("bandwidth_case") else 8
+        x = decode_inputs(dev, B, L, Hq, Hkv, T, tag.startswith("bandwidth_case"))
+        q, k, v, ck, cv, idx, sl, cl, seqlens, clen = (x[n] for n in ("q", "k", "v", "ck", "cv", "idx", "sl", "cl", "seqlens", "clen"))
+        d, bs, ks, st = x["d"], x["bs"], x["ks"], x["st"]
         sel_rows = sum(min(bs, int(seqlens[b]) - int(i) * bs) for b in range(B) for h in range(1) for i in idx[0, b].tolist() if i >= 0)
         work = {
             "flash_attention_decode": (lambda: ops.flash_attention_decode(q, k, v, sl), 4 * int(seqlens.sum()) * Hkv * d),
@@ -855,6 +875,8 @@ def main():
     ap.add_argument("--topk", type=int, default=None, help="override the number of selected blocks (size sweep only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode-operator micro-benchmark")
+    ap.add_argument("--decode-profile", action="store_true",
+                    help="only run the three decode operators twice each on the bandwidth case (the input of an ncu capture)")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the legs beside the headline: reference on the GPU, size sweep, generation, strong scaling")
     args = ap.parse_args()
@@ -876,6 +898,9 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    if args.decode_profile:
+        decode_profile_case(ops, dev)
+        return
     dist = None
     if world > 1:
         import torch.distributed as dist
