@@ -62,6 +62,17 @@ def kv_head_range(rank: int, world_size: int, num_kv_heads: int) -> Tuple[int, i
     return rank * per, (rank + 1) * per
 
 
+def _all_gather_rows(gathered: torch.Tensor, local: torch.Tensor, group) -> None:
+    """gathered[r] = rank r's `local`, in one collective where the backend has one (NCCL); the gloo backend of the CPU tests
+    takes the list form over views of the same buffer."""
+    import torch.distributed as dist
+
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather_into_tensor(gathered, local, group=group)
+    else:
+        dist.all_gather(list(gathered.unbind(0)), local, group=group)
+
+
 def gather_varlen(local: torch.Tensor, parts: List[List[int]], cu_seqlens: torch.Tensor, group=None) -> torch.Tensor:
     """All-gather the per-rank outputs of a sequence-sharded operator back into the original token order."""
     import torch.distributed as dist
@@ -70,11 +81,16 @@ def gather_varlen(local: torch.Tensor, parts: List[List[int]], cu_seqlens: torch
     cu = cu_seqlens.tolist()
     sizes = [sum(cu[i + 1] - cu[i] for i in ids) for ids in parts]
     mx = max(sizes) if sizes else 0
-    pad = local.new_zeros((mx,) + tuple(local.shape[1:]))
-    pad[: local.shape[0]] = local
-    bufs = [torch.empty_like(pad) for _ in range(world)]
-    dist.all_gather(bufs, pad, group=group)
-    return unshard_varlen([b[:s] for b, s in zip(bufs, sizes)], parts, cu_seqlens)
+    if local.shape[0] == mx:
+        pad = local.contiguous()
+    else:
+        pad = local.new_zeros((mx,) + tuple(local.shape[1:]))
+        pad[: local.shape[0]] = local
+    # one collective into one buffer [world, mx, ...]: NCCL lands every rank's rows in local memory, then they are put in
+    # token order (a rank's sequences are not contiguous in the original batch)
+    gathered = local.new_empty((world, mx) + tuple(local.shape[1:]))
+    _all_gather_rows(gathered, pad, group)
+    return unshard_varlen([gathered[r, :s] for r, s in enumerate(sizes)], parts, cu_seqlens)
 
 
 def gather_heads(local: torch.Tensor, group=None) -> torch.Tensor:
@@ -82,6 +98,8 @@ def gather_heads(local: torch.Tensor, group=None) -> torch.Tensor:
     import torch.distributed as dist
 
     world = dist.get_world_size(group)
-    bufs = [torch.empty_like(local) for _ in range(world)]
-    dist.all_gather(bufs, local.contiguous(), group=group)
-    return torch.cat(bufs, dim=1)
+    local = local.contiguous()
+    gathered = local.new_empty((world,) + tuple(local.shape))
+    _all_gather_rows(gathered, local, group)
+    # [world, tokens, heads_local, d] -> [tokens, world * heads_local, d]
+    return gathered.permute(1, 0, 2, 3).reshape(local.shape[0], world * local.shape[1], local.shape[2])
