@@ -9,8 +9,12 @@ followed, so a test may also evaluate it on a GPU in true fp32) what the referen
 (XunhaoLai/native-sparse-attention-triton) computes.  The reference file and
 lines each function follows are cited in its docstring (paths are relative to
 the reference project root).  The restatement is pinned against the reference's
-own ``ops.torch`` implementations by the fixtures in ``tests/golden`` (made by
-``tests/golden/make_golden.py``, which imports the reference).
+own ``ops.torch`` implementations by the fixtures in ``tests/golden`` made by
+``tests/golden/make_golden.py`` (which imports the reference on the CPU), and
+against the reference ITSELF run on a B200 -- its Triton operators, the
+flash_attn call of its sliding-window branch, its RotaryEmbedding, its nsa_infer
+with its NSACache -- by the ``box_*.npz`` fixtures made by
+``tests/golden/make_golden_on_box.py``.
 
 All functions are differentiable torch code, so gradients for the backward
 parity tests come from autograd over these fp32 formulas.
@@ -525,7 +529,7 @@ def total_useful_flops(seqlens, Hq, Hkv, d, kernel_size, kernel_stride, block_si
 def gate_combine(gate, o_cmp, o_sel, o_win):
     """Gated sum of the three branch outputs, gate [n, h, 3], o_* [n, h, d]: the expression of the reference's layer
     (native_sparse_attention/module/native_sparse_attention.py:226-232, infer/nsa_inference.py:146-150) evaluated in fp32.
-    No test of the reference pins this step (its layer scripts only run); parity unpinned beyond the expression itself."""
+    Pinned as part of the inference step (tests/golden/box_infer_*.npz: the reference's nsa_infer run on a B200)."""
     g = gate.float()
     out = g[..., 0:1] * o_cmp.float() + g[..., 1:2] * o_sel.float() + g[..., 2:3] * o_win.float()
     return out.to(o_cmp.dtype)
@@ -536,9 +540,8 @@ def rope(x, inv_freq, cu_seqlens, step=0, stride=1, attention_scaling=1.0):
     cat(-x2, x1) (native_sparse_attention/module/rope.py:36-41,204-209); cos/sin of the fp32 angle inv_freq * position,
     times attention_scaling, rounded to x.dtype (:126-155); position t * stride for the t-th token of a sequence when
     step == 0, (seqlen_b + step - 1) * stride for row b when step > 0 (:158-195).  The arithmetic after the table lookup is
-    fp32 here (the reference rounds each product to x.dtype).  The reference's module cannot be imported without a GPU
-    (rope.py:74 calls torch.cuda.current_device() in a default argument) and its tests hold no vectors for it: parity
-    unpinned beyond this restatement."""
+    fp32 here (the reference rounds each product to x.dtype).  Pinned by tests/golden/box_rope.npz: outputs of the
+    reference's RotaryEmbedding on a B200 (llama3 scaling, prefill / strided / decode positions, bf16 and fp16)."""
     lens = (cu_seqlens[1:] - cu_seqlens[:-1]).tolist()
     if step == 0:
         pos = torch.cat([torch.arange(n) for n in lens]) if lens else torch.zeros(0, dtype=torch.long)

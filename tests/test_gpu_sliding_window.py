@@ -1,7 +1,8 @@
 """Sliding-window branch (causal attention over keys t - W .. t): forward and backward parity with the fp32 CPU oracle.
 
-The reference delegates this branch to flash_attn (module/native_sparse_attention.py:213-223) and stores no vectors for
-it, so the oracle's restatement of the mask is the only pin (parity unpinned by the reference)."""
+The reference delegates this branch to flash_attn (module/native_sparse_attention.py:213-223); the oracle's restatement of
+its mask is pinned by tests/golden/box_window.npz (flash_attn's own output on a B200, tests/test_oracle_box_golden.py), and
+tests/test_gpu_box_golden.py compares these kernels with that file directly."""
 import pytest
 import torch
 

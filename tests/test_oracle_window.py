@@ -1,5 +1,6 @@
-"""CPU checks of the oracle's sliding-window attention (the branch the reference delegates to flash_attn and pins with no
-vectors): against a loop over single queries, and against the oracle's own causal attention when the window covers all."""
+"""CPU checks of the oracle's sliding-window attention (the branch the reference delegates to flash_attn): against a loop
+over single queries, and against the oracle's own causal attention when the window covers all.  The pin against flash_attn's
+own output is tests/test_oracle_box_golden.py."""
 import math
 
 import torch
