@@ -158,14 +158,38 @@ def nsa_infer(cu_seqlens: torch.Tensor, step: int, query: torch.Tensor, key: tor
         key = rope(key, cu_seqlens, step)
     cache.update_kv(cu_seqlens, step, compress_key, compress_value, key, value, key, value)
     seqlens = cache.sparse_kv_len[:batch]  # counts the new token
+    # The sliding-window branch depends on neither of the other two.  While the step is being captured into a CUDA graph
+    # it is put on a second stream (fork / join), so that a replay runs it beside the compressed -> selected chain: each of
+    # these kernels occupies a dozen SMs.  Launched eagerly the step stays on one stream (the host is the bound there).
+    main = torch.cuda.current_stream(query.device)
+    fork = torch.cuda.is_current_stream_capturing()
+    if fork:
+        side = _side_stream(query.device)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            o_win = ops.flash_attention_decode(query, cache.sliding_kv_cache[0, :batch], cache.sliding_kv_cache[1, :batch],
+                                               torch.clamp(cache.sliding_kv_len[:batch], max=window_size))
     o_cmp, topk_idx = ops.compressed_attention_decode(query, cache.compress_kv_cache[0, :batch], cache.compress_kv_cache[1, :batch],
                                                       seqlens, cache.compress_kv_len[:batch], kernel_size, kernel_stride,
                                                       block_size, topk, init_blocks, local_blocks, max_seqlen=cache.max_length)
     o_sel = ops.topk_sparse_attention_decode(query, cache.sparse_kv_cache[0, :batch], cache.sparse_kv_cache[1, :batch], topk_idx,
                                              block_size, seqlens)
-    o_win = ops.flash_attention_decode(query, cache.sliding_kv_cache[0, :batch], cache.sliding_kv_cache[1, :batch],
-                                       torch.clamp(cache.sliding_kv_len[:batch], max=window_size))
+    if fork:
+        main.wait_stream(side)
+    else:
+        o_win = ops.flash_attention_decode(query, cache.sliding_kv_cache[0, :batch], cache.sliding_kv_cache[1, :batch],
+                                           torch.clamp(cache.sliding_kv_len[:batch], max=window_size))
     return ops.gate_combine(gate_value, o_cmp, o_sel, o_win)
+
+
+_side_streams = {}
+
+
+def _side_stream(device):
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device=device)
+    return _side_streams[key]
 
 
 class DecodeGraph:
