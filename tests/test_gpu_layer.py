@@ -67,6 +67,12 @@ def test_layer_forward_backward(Hq, Hkv, seqlens, topk, window):
     # compression weights, 2.5e-3 or less elsewhere).
     from tests.helpers import CHAIN_GRAD_MEAN_TOL, assert_close_16bit, grad_tol
     for n in names:
+        # d(pe) sums, over every compressed token, a gradient whose exact value nearly cancels (a common shift of all
+        # compressed keys is invisible to the softmax but for the rotation): what is left is mostly the summed rounding of
+        # dK, so it gets the key gradients' worst-element bound and a mean bound of 1e-2 (observed 5.5e-3 to 6.1e-3)
+        if n == "pe":
+            assert_close_16bit(t[n].grad, r[n].grad, "dpe", grad_tol("dk"), 1e-2)
+            continue
         assert_close_16bit(t[n].grad, r[n].grad, "d" + n, grad_tol("d" + n, chain=True), 1.5 * CHAIN_GRAD_MEAN_TOL)
     assert_close_16bit(gate_g.grad, gate_r.grad, "dgate", grad_tol("dgate", chain=True), 1.5 * CHAIN_GRAD_MEAN_TOL)
     assert status_ok()
