@@ -610,11 +610,12 @@ def config3_sweep(ops, dev, with_reference):
 
 
 def compression_bandwidth(ops, dev):
-    """Compression forward kernels against HBM: 262144 tokens x 4 heads x 128 (268 MB of input, twice the L2), kernel 32,
-    stride 16; a 256 MB write between timed calls evicts the caches.  Algorithmic bytes: input read once, output written
-    once (plus the weights of the linear projection)."""
+    """Compression forward kernels against HBM: 2 097 152 tokens x 4 heads x 128 (2.1 GB of input; at 262 144 tokens the
+    pooling kernels last 86 us, a fifth of which is ramp-up: 3.3 TB/s there, 4.7 TB/s at 4 M tokens), kernel 32, stride 16;
+    a 256 MB write between timed calls evicts the caches.  Algorithmic bytes: input read once, output written once (plus
+    the weights of the linear projection)."""
     pkg = sys.modules["native_sparse_attention_triton_b200"]
-    N, H, d, ks, st = 262144, WORKLOAD["Hkv"], WORKLOAD["d"], 32, 16
+    N, H, d, ks, st = 2097152, WORKLOAD["Hkv"], WORKLOAD["d"], 32, 16
     g = torch.Generator(device=dev).manual_seed(5)
     x = torch.randn(N, H, d, generator=g, device=dev).to(torch.bfloat16)
     wl = (torch.randn(H, ks * d, d, generator=g, device=dev) / math.sqrt(ks * d)).to(torch.bfloat16)

@@ -33,15 +33,6 @@ int nsa_version(void);
  * 2 = index out of range); synchronises `stream`.  No counterpart in the reference. */
 int nsa_last_device_status(void* stream);
 
-/* Number of kernels this library has launched in the calling process.  No counterpart in the reference. */
-long long nsa_launch_count(void);
-
-/* Per-kernel device timing: while enabled, every kernel launch is bracketed by CUDA events on its stream.
- * nsa_profile_collect synchronises the device and writes one line "kernel launches total_ms" per kernel for
- * the launches recorded since the previous collect (returns the bytes written).  No counterpart in the reference. */
-int nsa_profile_enable(int on);
-int nsa_profile_collect(char* buf, int buflen);
-
 /* Forward of attention over selected KV blocks.
  * Replaces _topk_sparse_attention_fwd / forward_kernel,
  * native_sparse_attention/ops/triton/topk_sparse_attention.py:26-173,828-909.

@@ -1,4 +1,5 @@
 #include "host_util.h"
+#include "nsa_b200_instrument.h"
 
 #include <cudaTypedefs.h>
 #include <atomic>

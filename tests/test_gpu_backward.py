@@ -88,8 +88,9 @@ def test_compressed_attention_backward(ops, Hq, Hkv, d, seqlens, topk):
 
 
 @pytest.mark.parametrize("causal", [False, True])
-def test_flash_attention_backward(ops, causal):
-    x = chain_inputs(5, [100, 333, 64], 8, 2, 64, 32)
+@pytest.mark.parametrize("Hq,Hkv,d", [(8, 2, 64), (32, 2, 128), (8, 8, 128)])   # G = 4 / 16 / 1, both head sizes
+def test_flash_attention_backward(ops, causal, Hq, Hkv, d):
+    x = chain_inputs(5, [100, 333, 64], Hq, Hkv, d, 32)
     g = torch.Generator().manual_seed(7)
     cu = x["cu"]
     do = torch.randn(x["q"].shape, generator=g).bfloat16().float()

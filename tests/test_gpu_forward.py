@@ -138,8 +138,9 @@ def test_chain_forward_random(ops, Hq, Hkv, d, seqlens, topk):
 
 
 @pytest.mark.parametrize("causal", [False, True])
-def test_flash_attention_varlen_forward(ops, causal):
-    x = chain_inputs(5, [100, 333, 64], 8, 2, 64, 32)
+@pytest.mark.parametrize("Hq,Hkv,d", [(8, 2, 64), (32, 2, 128), (8, 8, 128)])   # G = 4 / 16 / 1, both head sizes
+def test_flash_attention_varlen_forward(ops, causal, Hq, Hkv, d):
+    x = chain_inputs(5, [100, 333, 64], Hq, Hkv, d, 32)
     cu = x["cu"].cuda()
     o = ops.flash_attention_varlen(dev(x["q"]), dev(x["k"]), dev(x["v"]), cu, cu, 333, 333, causal)
     o_ref = O.flash_attention_varlen(x["q"], x["k"], x["v"], x["cu"], x["cu"], causal=causal)
