@@ -182,6 +182,12 @@ def grad_tol(name, chain=False):
         return KV_GRAD_MAX_TOL / 2
     if chain and name == "dq":
         return 2 * MAX_TOL   # the sum of two operators' query gradients, each within MAX_TOL (1.5e-2 measured)
+    if chain and name == "dgate":
+        # an element is the dot product over head_dim of dO with a branch output, which the layer (like the reference's)
+        # holds rounded to 16 bits and the oracle in fp32.  For the first tokens of a sequence |o| ~ 1, so the rounding alone
+        # has a standard deviation of sqrt(128) * 2^-9 / sqrt(3) = 1.3e-2 per element; the largest of ~1e5 elements sits near
+        # 4.5 sigma (2.0e-2 and 4.1e-2 measured on the two layer cases).  Six sigma:
+        return KV_GRAD_MAX_TOL
     return MAX_TOL
 
 
