@@ -866,6 +866,49 @@ def strong_scaling(ops, dev, rank, world, dist):
 
 
 
+def step_timeline(ops, t, cu, max_q, max_k):
+    """Device timeline of one step (`--timeline`): every kernel, memset and copy of the middle one of three steps recorded
+    by torch.profiler, summarised as the span of the step, the time the device was busy, the idle gaps between activities,
+    and how the busy time splits into this library's kernels, memsets and torch's own kernels (autograd's accumulation of
+    the two query gradients, index arithmetic).  Taken under a tracer: it explains `ms_per_step`, it is not a bench value."""
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            chain_step(ops, t, cu, max_q, max_k)
+        torch.cuda.synchronize()
+    ev = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                key=lambda e: e.time_range.start)
+    marks = [i for i, e in enumerate(ev) if "linear_bias" in e.name]   # the first launch of a step
+    if len(marks) < 3:
+        return dict(error="step boundaries not found in the trace")
+    step = ev[marks[1]:marks[2]]
+    groups = dict(library_kernels=0.0, memsets=0.0, copies=0.0, torch_kernels=0.0)
+    other = {}
+    busy = gaps = 0.0
+    end = step[0].time_range.start
+    for e in step:
+        dur = e.time_range.end - e.time_range.start
+        gaps += max(0.0, e.time_range.start - end)
+        end = max(end, e.time_range.end)
+        busy += dur
+        if "nsa::" in e.name:
+            groups["library_kernels"] += dur
+        elif e.name.startswith("Memset"):
+            groups["memsets"] += dur
+        elif e.name.startswith("Memcpy"):
+            groups["copies"] += dur
+        else:
+            groups["torch_kernels"] += dur
+            key = e.name.split("<")[0].split("(")[0].replace("void ", "")[:60]
+            other[key] = other.get(key, 0.0) + dur
+    top_other = sorted(other.items(), key=lambda kv: -kv[1])[:4]
+    return dict(span_ms=(ev[marks[2]].time_range.start - step[0].time_range.start) / 1e3, busy_ms=busy / 1e3,
+                idle_gaps_ms=gaps / 1e3, activities=len(step), **{k + "_ms": v / 1e3 for k, v in groups.items()},
+                largest_torch_kernels_ms={k: v / 1e3 for k, v in top_other},
+                what="one step under torch.profiler (CUPTI activity trace); explains ms_per_step, not a bench value")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -878,6 +921,8 @@ def main():
     ap.add_argument("--no-decode", action="store_true", help="skip the decode-operator micro-benchmark")
     ap.add_argument("--decode-profile", action="store_true",
                     help="only run the three decode operators twice each on the bandwidth case (the input of an ncu capture)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="add `step_timeline`: where one step's device time goes (library kernels, memsets, torch kernels, gaps)")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the legs beside the headline: reference on the GPU, size sweep, generation, strong scaling")
     args = ap.parse_args()
@@ -953,6 +998,8 @@ def main():
         chain_step(ops, t, cu, max_q, max_k)
     prof = pkg._lib.profile_collect()
     pkg._lib.profile(False)
+
+    timeline = step_timeline(ops, t, cu, max_q, max_k) if (args.timeline and rank == 0) else None
 
     # ---------------- end to end: host buffers -> device, step, loss back to the host ----------------
     # Two sets of device inputs: the copy of step s+1 (its own stream) runs under the compute of step s, as a training
@@ -1111,7 +1158,7 @@ def main():
                 frac_of_tc_peak=useful_tflops / pk["tc_sustained"], per_kernel_ms=per_kernel, kernel_rooflines=kernel_rooflines, decode=decode, sliding_window=window, gate_combine=combine, rope=rope, decode_step=decode_step,
                 hbm_peak_gb_per_s=pk["hbm"], device_status=status, h2d_gb_per_s_per_rank=h2d_gbs,
                 strong_scaling=scaling_legs, gpu_reference=gpu_ref, config3_sweep=sweep, config5_generate=generate,
-                compression=compression,
+                compression=compression, step_timeline=timeline,
                 decode_tokens_per_s_per_gpu=(generate or {}).get("decode_tokens_per_s_per_gpu"))
     print(json.dumps(line), flush=True)
     if dist is not None:

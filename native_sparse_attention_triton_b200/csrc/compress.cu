@@ -172,7 +172,7 @@ struct PoolFwdParams {
   int B, H, D, ks, stride, M;
 };
 
-template <typename T>
+template <typename T, int TAPS>
 __global__ void __launch_bounds__(256) pool_fwd_kernel(PoolFwdParams p) {
   const int CH = p.D / 8;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -186,18 +186,18 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(PoolFwdParams p) {
   const T* x = static_cast<const T*>(p.x) + (long long)(__ldg(p.cu + b) + m * p.stride) * p.x_sn + (long long)h * p.x_sh + c * 8;
   const T* w = p.w ? static_cast<const T*>(p.w) + h * p.ks : nullptr;
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  // eight taps per step (kernel sizes are multiples of 16): eight independent 16-byte loads in flight per thread, which
-  // is what keeps HBM busy on long inputs and keeps the chain of dependent loads short on the few rows of a decode step
-  for (int k0 = 0; k0 < p.ks; k0 += 8) {
-    uint4 v[8];
-    float wv[8];
+  // TAPS taps per step (kernel sizes are multiples of 16): eight independent 16-byte loads in flight per thread keep HBM
+  // busy on long inputs; the few rows of a decode step take sixteen, so that a window costs one or two memory round trips
+  for (int k0 = 0; k0 < p.ks; k0 += TAPS) {
+    uint4 v[TAPS];
+    float wv[TAPS];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
+    for (int u = 0; u < TAPS; ++u) {
       v[u] = __ldg(reinterpret_cast<const uint4*>(x + (long long)(k0 + u) * p.x_sn));
       wv[u] = w ? DT<T>::to_float(w[k0 + u]) : 1.f;
     }
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
+    for (int u = 0; u < TAPS; ++u) {
       const uint32_t uu[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -254,7 +254,11 @@ static int launch_pool_fwd(PoolFwdParams p, const void* pe, void* bias_scratch, 
   }
   const long long total = (long long)p.M * p.H * (D / 8);
   const int blocks = (int)((total + 255) / 256);
-  { LaunchScope ls_("pool_compress_fwd", stream); pool_fwd_kernel<T><<<blocks, 256, 0, stream>>>(p); }
+  {
+    LaunchScope ls_("pool_compress_fwd", stream);
+    if (blocks <= 148) pool_fwd_kernel<T, 16><<<blocks, 256, 0, stream>>>(p);   // latency-bound: fewer, wider steps
+    else pool_fwd_kernel<T, 8><<<blocks, 256, 0, stream>>>(p);
+  }
   return cuda_rc(cudaGetLastError());
 }
 
@@ -287,6 +291,7 @@ extern "C" int nsa_pool_compress_fwd(const void* x, const void* w, const void* p
   if (!x || !cu_seqlens || !y_cu_seqlens || batch <= 0 || num_heads <= 0) return kInvalid;
   if (pe && !bias_scratch) return kInvalid;
   if (kernel_size <= 0 || kernel_stride <= 0 || kernel_size % kernel_stride) return kInvalid;
+  if (kernel_size % 16) return kUnsupported;  // the kernel reads sixteen or eight taps per step
   if (total_y <= 0) return kOk;
   if (!y) return kInvalid;
   if ((x_stride_n | x_stride_h) % 8 || !aligned16(x) || !aligned16(y)) return kInvalid;

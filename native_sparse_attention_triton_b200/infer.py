@@ -224,7 +224,11 @@ class DecodeGraph:
                 cache.sliding_kv_cache, cache.sliding_kv_len)
 
     def __call__(self, query, key, value, gate_value):
-        for dst, src in zip(self.inputs, (query, key, value, gate_value)):
-            dst.copy_(src)
+        srcs = [query, key, value, gate_value]
+        if all(s.dtype == d.dtype and s.device == d.device and s.shape == d.shape for s, d in zip(srcs, self.inputs)):
+            torch._foreach_copy_(self.inputs, srcs)   # one launch for the four inputs
+        else:
+            for dst, src in zip(self.inputs, srcs):
+                dst.copy_(src)
         self.graph.replay()
         return self.output

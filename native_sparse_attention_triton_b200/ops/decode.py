@@ -87,9 +87,9 @@ def flash_attention_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, se
     cache_len, num_kv_heads = k.shape[1], k.shape[2]
     if sm_scale is None:
         sm_scale = default_scale(head_dim)
-    o = torch.zeros_like(q)
     if cache_len == 0:
-        return o
+        return torch.zeros_like(q)
+    o = torch.empty_like(q)   # every row is written: a sequence without visible rows gets zeros from the kernel
     splits, scratch, n = _scratch(batch, num_kv_heads, head_dim, (cache_len + 63) // 64, q.device)
     torch.cuda.set_device(q.device)
     rc = _lib.lib().nsa_flash_attn_decode(ptr(q), ptr(k), ptr(v), ptr(seqlens), ptr(o), ptr(scratch), n, splits, batch,
@@ -117,9 +117,9 @@ def topk_sparse_attention_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tens
     topk = topk_idx.shape[-1]
     if sm_scale is None:
         sm_scale = default_scale(head_dim)
-    o = torch.zeros_like(q)
     if cache_len == 0:
-        return o
+        return torch.zeros_like(q)
+    o = torch.empty_like(q)   # every row is written: a sequence without visible rows gets zeros from the kernel
     splits, scratch, n = _scratch(batch, num_kv_heads, head_dim, topk * max(1, block_size // 64), q.device)
     torch.cuda.set_device(q.device)
     rc = _lib.lib().nsa_topk_sparse_attn_decode(ptr(q), ptr(k), ptr(v), ptr(topk_idx), ptr(seqlens), ptr(o),

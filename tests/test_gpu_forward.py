@@ -168,3 +168,29 @@ def test_decode_bandwidth_shapes(ops):
     o = ops.topk_sparse_attention_decode(dev(q), dev(k), dev(v), idx.cuda(), bs, seqlens.cuda())
     close(o, O.topk_sparse_attention_decode(q, k, v, idx, bs, seqlens), "sparse_decode")
     assert status_ok()
+
+
+def test_decode_rows_without_visible_keys_are_zero(ops):
+    """A sequence whose cache is still empty (seqlens 0), or whose selection is all padding, gets a zero output row from
+    the kernel itself: the wrappers hand it uninitialised memory to write into."""
+    g = torch.Generator().manual_seed(43)
+    B, L, Hq, Hkv, d, bs, T = 5, 256, 16, 2, 128, 64, 4
+    seqlens = torch.tensor([0, 1, 130, 0, 256], dtype=torch.int32)
+    q = torch.randn(B, Hq, d, generator=g).bfloat16().float()
+    k = torch.randn(B, L, Hkv, d, generator=g).bfloat16().float()
+    v = torch.randn(B, L, Hkv, d, generator=g).bfloat16().float()
+    live = seqlens > 0
+    for _ in range(2):   # the second call writes into memory the first one left non-zero
+        o = ops.flash_attention_decode(dev(q), dev(k), dev(v), seqlens.cuda())
+        assert float(o[~live.cuda()].float().abs().max()) == 0.0
+        close(o[live.cuda()], O.flash_attention_decode(q[live], k[live], v[live], seqlens[live]), "flash_decode")
+    idx = torch.full((Hkv, B, T), -1, dtype=torch.int32)
+    idx[:, 2, :3] = torch.tensor([0, 1, 2], dtype=torch.int32)
+    idx[:, 4, :2] = torch.tensor([1, 3], dtype=torch.int32)
+    picked = torch.tensor([False, False, True, False, True])
+    for _ in range(2):
+        o = ops.topk_sparse_attention_decode(dev(q), dev(k), dev(v), idx.cuda(), bs, seqlens.cuda())
+        assert float(o[~picked.cuda()].float().abs().max()) == 0.0
+        close(o[picked.cuda()], O.topk_sparse_attention_decode(q[picked], k[picked], v[picked], idx[:, picked], bs, seqlens[picked]),
+              "sparse_decode")
+    assert status_ok()
