@@ -77,11 +77,13 @@ int nsa_compressed_attn_topk(const void* q, const void* k, const float* lse, con
  * native_sparse_attention/ops/triton/linear_compress.py:26-136,309-417,497-525.
  *   x [N, H, d] (strides x_stride_n, x_stride_h), w [H, kernel_size*d, d] contiguous, pe [H, kernel_size, d]
  *   contiguous or NULL, y [total_y, H, d] contiguous, y_cu_seqlens int32 [batch+1],
- *   bias_scratch [H, d] of the storage type (needed iff pe != NULL). */
+ *   bias_scratch [H, d] of the storage type (needed iff pe != NULL); total_len = N, the rows of x (the bound of the
+ *   TMA views of x: head_dim 128 with at least 128 windows in some sequence runs as one tcgen05 GEMM per
+ *   (sequence, head) whose operands TMA fetches; other shapes on the warp-level tensor-core kernel). */
 int nsa_linear_compress_fwd(const void* x, const void* w, const void* pe, const int* cu_seqlens,
-                            const int* y_cu_seqlens, void* y, void* bias_scratch, int batch, int total_y,
-                            int max_y_len, int num_heads, int head_dim, int kernel_size, int kernel_stride,
-                            long long x_stride_n, long long x_stride_h, int dtype, void* stream);
+                            const int* y_cu_seqlens, void* y, void* bias_scratch, int total_len, int batch,
+                            int total_y, int max_y_len, int num_heads, int head_dim, int kernel_size,
+                            int kernel_stride, long long x_stride_n, long long x_stride_h, int dtype, void* stream);
 
 /* Weighted (w [H, kernel_size]) or average (w == NULL) pooling compression forward.
  * Replaces SlidingWindowWeightedPool.forward + the bias einsum/mean,

@@ -13,6 +13,7 @@
 #include "attn_tile.cuh"
 #include "dispatch.h"
 #include "host_util.h"
+#include "linear_fwd_tc.h"
 #include "nsa_b200.h"
 
 namespace nsa {
@@ -226,7 +227,8 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(PoolFwdParams p) {
 }
 
 template <typename T, int D>
-static int launch_linear_fwd(LinFwdParams p, const void* pe, void* bias_scratch, int B, int max_ylen, cudaStream_t stream) {
+static int launch_linear_fwd(LinFwdParams p, const void* pe, void* bias_scratch, int B, int max_ylen, int total_len, int dtype,
+                             cudaStream_t stream) {
   if (pe) {
     { LaunchScope ls_("linear_bias", stream); linear_bias_kernel<T><<<dim3(p.H, D / 8), 256, 0, stream>>>(
         static_cast<const T*>(pe), static_cast<const T*>(p.w), static_cast<T*>(bias_scratch), p.ks * D, D); }
@@ -234,6 +236,9 @@ static int launch_linear_fwd(LinFwdParams p, const void* pe, void* bias_scratch,
   } else {
     p.bias = nullptr;
   }
+  if (linear_fwd_tc_eligible(D, max_ylen, total_len, p.ks, p.stride))
+    return linear_fwd_tc(p.x, p.w, p.bias, p.y, p.cu, p.ycu, B, max_ylen, total_len, p.H, p.ks, p.stride, p.x_sn, p.x_sh, dtype,
+                         stream);
   const size_t smem = 1024 + 2 * (64 * D * 2 + D * D * 2);
   auto kern = linear_fwd_kernel<T, D>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -265,7 +270,7 @@ static int launch_pool_fwd(PoolFwdParams p, const void* pe, void* bias_scratch, 
 }  // namespace nsa
 
 extern "C" int nsa_linear_compress_fwd(const void* x, const void* w, const void* pe, const int* cu_seqlens,
-                                       const int* y_cu_seqlens, void* y, void* bias_scratch, int batch,
+                                       const int* y_cu_seqlens, void* y, void* bias_scratch, int total_len, int batch,
                                        int total_y, int max_y_len, int num_heads, int head_dim, int kernel_size,
                                        int kernel_stride, long long x_stride_n, long long x_stride_h, int dtype,
                                        void* stream) {
@@ -279,7 +284,7 @@ extern "C" int nsa_linear_compress_fwd(const void* x, const void* w, const void*
   LinFwdParams p;
   p.x = x; p.w = w; p.bias = nullptr; p.y = y; p.cu = cu_seqlens; p.ycu = y_cu_seqlens;
   p.x_sn = x_stride_n; p.x_sh = x_stride_h; p.H = num_heads; p.ks = kernel_size; p.stride = kernel_stride;
-  return NSA_DISPATCH_T_D(dtype, head_dim, launch_linear_fwd, p, pe, bias_scratch, batch, max_y_len,
+  return NSA_DISPATCH_T_D(dtype, head_dim, launch_linear_fwd, p, pe, bias_scratch, batch, max_y_len, total_len, dtype,
                           static_cast<cudaStream_t>(stream));
 }
 

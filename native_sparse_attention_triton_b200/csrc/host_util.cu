@@ -39,13 +39,13 @@ int make_tmap_3d(CUtensorMap* out, CUtensorMapDataType dt, const void* base, uin
 }
 
 int make_tmap_4d(CUtensorMap* out, CUtensorMapDataType dt, const void* base, uint64_t n0, uint64_t n1, uint64_t n2,
-                 uint64_t n3, uint64_t stride1, uint64_t stride2, uint64_t stride3, uint32_t b0, uint32_t b2) {
+                 uint64_t n3, uint64_t stride1, uint64_t stride2, uint64_t stride3, uint32_t b0, uint32_t b2, uint32_t b3) {
   std::call_once(g_encode_once, load_encode);
   if (!g_encode) return kUnsupported;
   if (!aligned16(base) || (stride1 * 2) % 16 || (stride2 * 2) % 16 || (stride3 * 2) % 16 || (b0 * 2) % 16) return kInvalid;
   cuuint64_t dims[4] = {n0, n1, n2, n3};
   cuuint64_t strides[3] = {stride1 * 2, stride2 * 2, stride3 * 2};
-  cuuint32_t box[4] = {b0, 1, b2, 1};
+  cuuint32_t box[4] = {b0, 1, b2, b3};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUtensorMapSwizzle sw = (b0 * 2 == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE;
   CUresult r = g_encode(out, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,

@@ -23,9 +23,10 @@ inline int cuda_rc(cudaError_t e) { return e == cudaSuccess ? 0 : 1000 + static_
 int make_tmap_3d(CUtensorMap* out, CUtensorMapDataType dt, const void* base, uint64_t n0, uint64_t n1, uint64_t n2,
                  uint64_t stride1, uint64_t stride2, uint32_t b0, uint32_t b1, uint32_t b2);
 
-// 4-D variant over [n3][n2][n1][n0]; box (b0, 1, b2, 1).
+// 4-D variant over [n3][n2][n1][n0]; box (b0, 1, b2, b3).
 int make_tmap_4d(CUtensorMap* out, CUtensorMapDataType dt, const void* base, uint64_t n0, uint64_t n1, uint64_t n2,
-                 uint64_t n3, uint64_t stride1, uint64_t stride2, uint64_t stride3, uint32_t b0, uint32_t b2);
+                 uint64_t n3, uint64_t stride1, uint64_t stride2, uint64_t stride3, uint32_t b0, uint32_t b2,
+                 uint32_t b3 = 1);
 
 // device status word of the current device (allocated on first use, zero-initialised)
 int* status_word();

@@ -56,7 +56,7 @@ class _Compress(torch.autograd.Function):
         torch.cuda.set_device(x.device)
         if mode == "linear":
             rc = lib.nsa_linear_compress_fwd(ptr(x), ptr(wc), ptr(pec), ptr(cu_seqlens), ptr(y_cu), ptr(y), ptr(bias),
-                                             batch, total_y, max_y, num_heads, head_dim, kernel_size, kernel_stride,
+                                             x.shape[0], batch, total_y, max_y, num_heads, head_dim, kernel_size, kernel_stride,
                                              x.stride(0), x.stride(1), dtype_code(x), stream_ptr(x.device))
             _lib.check(rc, "nsa_linear_compress_fwd")
         else:

@@ -194,3 +194,29 @@ def test_decode_rows_without_visible_keys_are_zero(ops):
         close(o[picked.cuda()], O.topk_sparse_attention_decode(q[picked], k[picked], v[picked], idx[:, picked], bs, seqlens[picked]),
               "sparse_decode")
     assert status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("H,seqlens,ks,st", [
+    (2, [5000, 37, 2992], 32, 16),     # 8029 tokens: the last windows end in the 13 tokens only the shifted TMA view reaches
+    (4, [4103], 64, 16),               # one sequence, four taps per stride group
+    (2, [300, 4500], 16, 16),          # windows that do not overlap
+    (1, [6000, 129], 32, 8),           # stride 8; a short sequence after a long one
+])
+def test_linear_compress_tensor_core_path(ops, dtype, H, seqlens, ks, st):
+    """head_dim 128 with at least 128 windows in a sequence and enough tokens runs as one tcgen05 GEMM per (sequence, head)
+    whose operands TMA fetches through a [token / stride][token % stride] view of x: against the oracle, with and without
+    the position embedding, and on a strided view of x (heads sliced out of a wider tensor)."""
+    d = 128
+    x = chain_inputs(77 + ks + st, seqlens, H, H, d, ks)
+    cu = x["cu"].cuda()
+    wide = torch.randn(sum(seqlens), H + 2, d, generator=torch.Generator().manual_seed(3)).to(dtype).cuda()
+    wide[:, 1:H + 1] = dev(x["k"], dtype)
+    for src, w, pe in ((dev(x["k"], dtype), x["wk"], x["pe"]), (wide[:, 1:H + 1], x["wk"], x["pe"]), (dev(x["v"], dtype), x["wv"], None)):
+        y, y_cu = ops.linear_compress(src, dev(w, dtype), cu, ks, st, dev(pe, dtype) if pe is not None else None)
+        ref_in = x["v"] if pe is None else x["k"]
+        y_ref, y_cu_ref = O.linear_compress(ref_in.to(dtype).float(), w.to(dtype).float(), x["cu"], ks, st,
+                                            pe.to(dtype).float() if pe is not None else None)
+        assert torch.equal(y_cu.cpu(), y_cu_ref.to(torch.int32))
+        close(y, y_ref, "linear_compress")
+    assert status_ok()
