@@ -1020,12 +1020,17 @@ def main():
     e0.record()
     copy_stream.wait_stream(main_stream)
 
+    copy_begin = [torch.cuda.Event(enable_timing=True) for _ in range(e2e_steps)]
+    copy_end = [torch.cuda.Event(enable_timing=True) for _ in range(e2e_steps)]
+
     def enqueue_copy(sidx):
         with torch.cuda.stream(copy_stream), torch.no_grad():
             if sidx >= 2:
                 copy_stream.wait_event(freed[sidx - 2])   # the step that used this set has finished with it
+            copy_begin[sidx].record(copy_stream)
             for n in host:
                 sets[sidx % 2][n].copy_(host[n], non_blocking=True)
+            copy_end[sidx].record(copy_stream)
             copied[sidx].record(copy_stream)
 
     enqueue_copy(0)
@@ -1041,6 +1046,8 @@ def main():
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    # the copies alone, as they ran under the previous step's compute (the first one ran alone)
+    e2e_copy_ms = [copy_begin[i].elapsed_time(copy_end[i]) for i in range(e2e_steps)]
     e2e_t = torch.tensor([e2e_ms], device=dev)
     if dist is not None:
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
@@ -1152,7 +1159,8 @@ def main():
                 ms_per_step=ms, higher_is_better=False, scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
                 config=config_record(), clocks=clocks,
                 e2e=dict(value=e2e_ms, unit="ms", h2d_bytes_per_step=h2d_bytes, d2h_bytes_per_step=4, steps=e2e_steps,
-                         note="host->device copy of step s+1 overlaps the compute of step s (two input sets)"),
+                         note="host->device copy of step s+1 overlaps the compute of step s (two input sets)",
+                         copy_ms_per_step_rank0=[round(x, 2) for x in e2e_copy_ms]),
                 gpu_launches=launches, roofline=roofline, cpu_baseline=cpu,
                 tokens_per_s=world * N / (ms / 1e3), useful_tflops_per_gpu=useful_tflops,
                 frac_of_tc_peak=useful_tflops / pk["tc_sustained"], per_kernel_ms=per_kernel, kernel_rooflines=kernel_rooflines, decode=decode, sliding_window=window, gate_combine=combine, rope=rope, decode_step=decode_step,
