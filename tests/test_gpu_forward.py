@@ -220,3 +220,21 @@ def test_linear_compress_tensor_core_path(ops, dtype, H, seqlens, ks, st):
         assert torch.equal(y_cu.cpu(), y_cu_ref.to(torch.int32))
         close(y, y_ref, "linear_compress")
     assert status_ok()
+
+
+def test_linear_compress_two_row_tiles_per_cta(ops):
+    """Problems of several waves of CTAs run with two 128-window row tiles per CTA sharing every weight tile: 310 005 tokens,
+    four heads, the last windows ending on the last token (shifted TMA view).  The oracle runs on the GPU in fp32."""
+    H, d, ks, st = 4, 128, 32, 16
+    seqlens = [200005, 110000]
+    g = torch.Generator().manual_seed(91)
+    N = sum(seqlens)
+    x = torch.randn(N, H, d, generator=g).bfloat16()
+    w = (torch.randn(H, ks * d, d, generator=g) / (ks * d) ** 0.5).bfloat16()
+    pe = (torch.randn(H, ks, d, generator=g) * 0.02).bfloat16()
+    cu = torch.tensor([0, seqlens[0], N], dtype=torch.int32).cuda()
+    y, y_cu = ops.linear_compress(x.cuda(), w.cuda(), cu, ks, st, pe.cuda())
+    y_ref, y_cu_ref = O.linear_compress(x.cuda().float(), w.cuda().float(), cu, ks, st, pe.cuda().float())
+    assert torch.equal(y_cu.cpu(), y_cu_ref.cpu().to(torch.int32))
+    close(y, y_ref, "linear_compress")
+    assert status_ok()
