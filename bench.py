@@ -407,6 +407,26 @@ def decode_profile_case(ops, dev):
     print(json.dumps(dict(decode_profile="ok")))
 
 
+def compress_profile_case(ops, dev):
+    """The three compression operators on 1 048 576 tokens x 4 heads x 128 (1.07 GB of input: larger than L2, small enough for
+    a profiler to replay), a cache-evicting write before each call; two rounds, the second one warm."""
+    N, H, d, ks, st = 1048576, WORKLOAD["Hkv"], WORKLOAD["d"], 32, 16
+    g = torch.Generator(device=dev).manual_seed(5)
+    x = torch.randn(N, H, d, generator=g, device=dev).to(torch.bfloat16)
+    wl = (torch.randn(H, ks * d, d, generator=g, device=dev) / math.sqrt(ks * d)).to(torch.bfloat16)
+    wp = (torch.rand(H, ks, generator=g, device=dev) / ks).to(torch.bfloat16)
+    pe = (torch.randn(H, ks, d, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    cu = torch.tensor([0, N], dtype=torch.int32, device=dev)
+    flush = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.float32, device=dev)
+    with torch.no_grad():
+        for _ in range(2):
+            for fn in (lambda: ops.weightedpool_compress(x, wp, cu, ks, st, pe), lambda: ops.linear_compress(x, wl, cu, ks, st, pe)):
+                flush.zero_()
+                fn()
+    torch.cuda.synchronize()
+    print(json.dumps(dict(compress_profile="ok")))
+
+
 def decode_microbench(ops, dev):
     """The three single-token operators on (a) the bandwidth-sized case of the reference's decode self-tests
     (batch 76, cache 8192, 32q/4kv heads, d=128, block 64, top-16, ragged lengths), (b) the same case with four times
@@ -921,6 +941,8 @@ def main():
     ap.add_argument("--no-decode", action="store_true", help="skip the decode-operator micro-benchmark")
     ap.add_argument("--decode-profile", action="store_true",
                     help="only run the three decode operators twice each on the bandwidth case (the input of an ncu capture)")
+    ap.add_argument("--compress-profile", action="store_true",
+                    help="run only the compression operators on a 1 M-token case (the case the profiler captures)")
     ap.add_argument("--timeline", action="store_true",
                     help="add `step_timeline`: where one step's device time goes (library kernels, memsets, torch kernels, gaps)")
     ap.add_argument("--no-extras", action="store_true",
@@ -946,6 +968,9 @@ def main():
     dev = torch.device("cuda", local)
     if args.decode_profile:
         decode_profile_case(ops, dev)
+        return
+    if args.compress_profile:
+        compress_profile_case(ops, dev)
         return
     dist = None
     if world > 1:

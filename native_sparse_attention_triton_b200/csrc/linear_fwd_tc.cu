@@ -2,13 +2,11 @@
 //
 //   y[m, :] = sum over taps of  x[s + m * stride + tap, :]  @  W[tap]        (W[tap] is [d x d], d = 128)
 //
-// A CTA owns TILES x 128 consecutive windows m of one (sequence, head) and walks the taps (two row tiles share every W[tap]
-// they fetch: the kernel is bound by the shared-memory fill, so large problems run with TILES = 2; small ones with one tile
-// per CTA to fill the SMs).  For a fixed tap the 128 rows it needs
+// A CTA owns 128 consecutive windows m of one (sequence, head) and walks the taps.  For a fixed tap the 128 rows it needs
 // are tokens `stride` apart: x is described to TMA as the 4-D tensor [token / stride][token % stride][head][d], so that a box
 // of 128 x 1 x 1 x 64 lands those rows densely in shared memory as a K-major, 128-byte-swizzled A panel.  W[tap] arrives
 // as two MN-major panels (rows = input feature = reduction index, 64 output features per panel row).  Eight
-// 128 x 128 x 16 products per tap and row tile accumulate into 128 TMEM columns per row tile; the epilogue rounds, adds the position-embedding
+// 128 x 128 x 16 products per tap accumulate into 128 TMEM columns; the epilogue rounds, adds the position-embedding
 // bias in the storage type (as the reference adds its einsum) and stores 16-byte chunks.
 //
 // The 4-D view covers floor(N / stride) * stride tokens.  The last N % stride tokens are reached through a second tensor
@@ -28,7 +26,7 @@ namespace nsa {
 namespace {
 constexpr int kLinD = 128;
 constexpr int kLinRows = 128;
-template <int TILES> struct LinStages { static constexpr int value = TILES == 1 ? 3 : 2; };
+constexpr int kLinStages = 3;
 constexpr int kLinPanel = 128 * 128;       // bytes: 128 rows of 64 16-bit elements
 constexpr int kLinTile = 2 * kLinPanel;    // one operand of one tap
 
@@ -43,16 +41,14 @@ struct LinTcParams {
 };
 }  // namespace
 
-template <typename T, int TILES>
+template <typename T>
 __global__ void __launch_bounds__(192, 1)
 linear_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmXa, const __grid_constant__ CUtensorMap tmXb,
                      const __grid_constant__ CUtensorMap tmW, LinTcParams p) {
-  constexpr int kLinStages = LinStages<TILES>::value;
-  constexpr int A_STAGE = TILES * kLinTile;
   extern __shared__ __align__(1024) uint8_t smem[];
-  uint8_t* a_sm = smem;                               // [stages][TILES][2 panels]
-  uint8_t* b_sm = smem + kLinStages * A_STAGE;        // [stages][2 panels]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kLinStages * (A_STAGE + kLinTile));
+  uint8_t* a_sm = smem;                               // [stages][2 panels]
+  uint8_t* b_sm = smem + kLinStages * kLinTile;       // [stages][2 panels]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * kLinStages * kLinTile);
   uint64_t* full = bars;
   uint64_t* empty = bars + kLinStages;
   uint64_t* acc_full = empty + kLinStages;
@@ -63,14 +59,12 @@ linear_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmXa, const __grid_cons
     if (threadIdx.x == 0) p.st.raise(kErrSmemLayout);
     return;
   }
-  // heads vary fastest over the grid: CTAs that run together read the same tokens' rows (adjacent in DRAM) for different heads
-  const int b = blockIdx.y, h = blockIdx.x % p.H;
+  const int b = blockIdx.y, h = blockIdx.z;
   const int s0 = __ldg(p.cu + b);
   const int y0 = __ldg(p.ycu + b), Mb = __ldg(p.ycu + b + 1) - y0;
-  const int m0 = (blockIdx.x / p.H) * (kLinRows * TILES);
+  const int m0 = blockIdx.x * kLinRows;
   if (m0 >= Mb) return;
-  const int rows = min(kLinRows * TILES, Mb - m0);
-  const int tiles = (rows + kLinRows - 1) / kLinRows;   // row tiles of this CTA that hold a window
+  const int rows = min(kLinRows, Mb - m0);
   // which view of x: the shifted one iff a stored row reads a token beyond the first view
   int tok0 = s0 + m0 * p.stride;
   const bool shifted = tok0 + (rows - 1) * p.stride + p.ks - 1 >= p.groups * p.stride;
@@ -90,7 +84,7 @@ linear_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmXa, const __grid_cons
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 128 * TILES);
+    tmem_alloc(tmem_slot, 128);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -104,13 +98,11 @@ linear_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmXa, const __grid_cons
       for (int tap = 0; tap < p.ks; ++tap) {
         const int s = tap % kLinStages;
         if (tap >= kLinStages && !mbar_wait(empty + s, ((tap / kLinStages) - 1) & 1, p.st)) break;
-        mbar_expect_tx(full + s, (tiles + 1) * kLinTile);
+        mbar_expect_tx(full + s, 2 * kLinTile);
         const int tok = tok0 + tap;
         const int g0 = tok / p.stride, j = tok - g0 * p.stride;
-        for (int t = 0; t < tiles; ++t)
 #pragma unroll
-          for (int pn = 0; pn < 2; ++pn)
-            tma_load_4d(a_sm + s * A_STAGE + t * kLinTile + pn * kLinPanel, tmX, full + s, pn * 64, h, j, g0 + t * kLinRows);
+        for (int pn = 0; pn < 2; ++pn) tma_load_4d(a_sm + s * kLinTile + pn * kLinPanel, tmX, full + s, pn * 64, h, j, g0);
 #pragma unroll
         for (int pn = 0; pn < 2; ++pn) tma_load_3d(b_sm + s * kLinTile + pn * kLinPanel, &tmW, full + s, pn * 64, tap * kLinD, h);
       }
@@ -124,14 +116,11 @@ linear_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmXa, const __grid_cons
       if (!mbar_wait(full + s, (tap / kLinStages) & 1, p.st)) break;
       tc_fence_after_sync();
       if (elect_one()) {
-        const uint32_t b_addr = b_base + s * kLinTile;
-        for (int t = 0; t < tiles; ++t) {
-          const uint32_t a_addr = a_base + s * A_STAGE + t * kLinTile;
+        const uint32_t a_addr = a_base + s * kLinTile, b_addr = b_base + s * kLinTile;
 #pragma unroll
-          for (int kk = 0; kk < kLinD / 16; ++kk)
-            umma_ss(tmem + t * 128, umma_desc_kmajor(a_addr + (kk >> 2) * kLinPanel + (kk & 3) * 32),
-                    umma_desc_mnmajor(b_addr + kk * 2048, kLinPanel), idesc, tap > 0 || kk > 0);
-        }
+        for (int kk = 0; kk < kLinD / 16; ++kk)
+          umma_ss(tmem, umma_desc_kmajor(a_addr + (kk >> 2) * kLinPanel + (kk & 3) * 32),
+                  umma_desc_mnmajor(b_addr + kk * 2048, kLinPanel), idesc, tap > 0 || kk > 0);
         umma_commit(empty + s);
       }
       __syncwarp();
@@ -141,16 +130,15 @@ linear_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmXa, const __grid_cons
   } else {
     // ===================== epilogue: thread = one window =====================
     const int quarter = warp & 3;  // the TMEM lanes a warp may read
+    const int r = quarter * 32 + lane;
     mbar_wait(acc_full, 0, p.st);
     tc_fence_after_sync();
-    const T* bias = p.bias ? static_cast<const T*>(p.bias) + (size_t)h * kLinD : nullptr;
-    for (int t = 0; t < tiles; ++t) {
-    const int r = t * kLinRows + quarter * 32 + lane;
     T* yrow = static_cast<T*>(p.y) + ((size_t)(y0 + m0 + r) * p.H + h) * kLinD;
+    const T* bias = p.bias ? static_cast<const T*>(p.bias) + (size_t)h * kLinD : nullptr;
 #pragma unroll
     for (int c = 0; c < kLinD / 32; ++c) {
       uint32_t v[32];
-      tmem_ld32(tmem_addr(tmem, quarter * 32, t * 128 + c * 32), v);
+      tmem_ld32(tmem_addr(tmem, quarter * 32, c * 32), v);
       tmem_ld_wait();
       if (r < rows) {
 #pragma unroll
@@ -177,21 +165,17 @@ linear_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmXa, const __grid_cons
         }
       }
     }
-    }
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem, 128 * TILES);
-}
-
-// a CTA of `tiles` row tiles spans (128 * tiles - 1) * stride + ks tokens; with twice that many tokens in x a CTA that needs
-// the shifted view never also needs the first (N % stride) tokens
-static bool lin_tc_fits(int tiles, int total_len, int kernel_size, int kernel_stride) {
-  return (long long)total_len >= 2ll * (kLinRows * tiles * (long long)kernel_stride + kernel_size);
+  if (warp == 1) tmem_dealloc(tmem, 128);
 }
 
 bool linear_fwd_tc_eligible(int head_dim, int max_y_len, int total_len, int kernel_size, int kernel_stride) {
-  return head_dim == kLinD && max_y_len >= kLinRows && kernel_stride >= 1 && lin_tc_fits(1, total_len, kernel_size, kernel_stride);
+  // a CTA spans 127 * stride + ks tokens; with twice that many tokens in x a CTA that needs the shifted view never also
+  // needs the first (N % stride) tokens
+  return head_dim == kLinD && max_y_len >= kLinRows && kernel_stride >= 1 &&
+         (long long)total_len >= 2ll * (kLinRows * (long long)kernel_stride + kernel_size);
 }
 
 template <typename T, int D>
@@ -208,18 +192,13 @@ static int launch_linear_fwd_tc(const void* x, const void* w, int batch, int max
   if (rc) return rc;
   rc = make_tmap_3d(&tmW, DT<T>::kTmapType, w, kLinD, (uint64_t)p.ks * kLinD, p.H, kLinD, (uint64_t)p.ks * kLinD * kLinD, 64, 128, 1);
   if (rc) return rc;
-  // two row tiles per CTA once single-tile CTAs would be several waves of the device anyway
-  const long long single = (long long)((max_y_len + kLinRows - 1) / kLinRows) * batch * p.H;
-  const bool two = single >= 4 * 148 && lin_tc_fits(2, total_len, p.ks, p.stride);
-  auto launch = [&](auto kern, int tiles, int stages) -> int {
-    const size_t smem = (size_t)stages * (tiles + 1) * kLinTile + (2 * stages + 1) * sizeof(uint64_t) + 16;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return cuda_rc(e);
-    dim3 grid((max_y_len + kLinRows * tiles - 1) / (kLinRows * tiles) * p.H, batch);
-    { LaunchScope ls_("linear_compress_fwd", stream); kern<<<grid, 192, smem, stream>>>(tmXa, tmXb, tmW, p); }
-    return cuda_rc(cudaGetLastError());
-  };
-  return two ? launch(linear_fwd_tc_kernel<T, 2>, 2, LinStages<2>::value) : launch(linear_fwd_tc_kernel<T, 1>, 1, LinStages<1>::value);
+  const size_t smem = 2 * kLinStages * kLinTile + (2 * kLinStages + 1) * sizeof(uint64_t) + 16;
+  auto kern = linear_fwd_tc_kernel<T>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return cuda_rc(e);
+  dim3 grid((max_y_len + kLinRows - 1) / kLinRows, batch, p.H);
+  { LaunchScope ls_("linear_compress_fwd", stream); kern<<<grid, 192, smem, stream>>>(tmXa, tmXb, tmW, p); }
+  return cuda_rc(cudaGetLastError());
 }
 
 int linear_fwd_tc(const void* x, const void* w, const void* bias, void* y, const int* cu, const int* ycu, int batch,

@@ -222,9 +222,9 @@ def test_linear_compress_tensor_core_path(ops, dtype, H, seqlens, ks, st):
     assert status_ok()
 
 
-def test_linear_compress_two_row_tiles_per_cta(ops):
-    """Problems of several waves of CTAs run with two 128-window row tiles per CTA sharing every weight tile: 310 005 tokens,
-    four heads, the last windows ending on the last token (shifted TMA view).  The oracle runs on the GPU in fp32."""
+def test_linear_compress_many_waves_of_ctas(ops):
+    """A problem of several waves of CTAs: 310 005 tokens, four heads, the last windows ending on the last token (shifted
+    TMA view).  The oracle runs on the GPU in fp32."""
     H, d, ks, st = 4, 128, 32, 16
     seqlens = [200005, 110000]
     g = torch.Generator().manual_seed(91)
