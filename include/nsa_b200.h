@@ -87,11 +87,14 @@ int nsa_linear_compress_fwd(const void* x, const void* w, const void* pe, const 
 
 /* Weighted (w [H, kernel_size]) or average (w == NULL) pooling compression forward.
  * Replaces SlidingWindowWeightedPool.forward + the bias einsum/mean,
- * native_sparse_attention/ops/triton/weighted_pool.py:23-85,182-239,301-363. */
+ * native_sparse_attention/ops/triton/weighted_pool.py:23-85,182-239,301-363.
+ *   Arguments as nsa_linear_compress_fwd (total_len = rows of x, max_y_len = longest compressed sequence).  Inputs of
+ *   8192 windows or more (head_dim 128) stream through shared memory in TMA chunks, every row fetched once; shorter ones
+ *   (and the single rows of a decode step) use one thread per window and 16-byte column group. */
 int nsa_pool_compress_fwd(const void* x, const void* w, const void* pe, const int* cu_seqlens,
-                          const int* y_cu_seqlens, void* y, void* bias_scratch, int batch, int total_y,
-                          int num_heads, int head_dim, int kernel_size, int kernel_stride,
-                          long long x_stride_n, long long x_stride_h, int dtype, void* stream);
+                          const int* y_cu_seqlens, void* y, void* bias_scratch, int total_len, int batch,
+                          int total_y, int max_y_len, int num_heads, int head_dim, int kernel_size,
+                          int kernel_stride, long long x_stride_n, long long x_stride_h, int dtype, void* stream);
 
 /* Number of split-KV partitions the decode kernels want for this problem (>= 1; max_tiles = 64-key tiles of the longest
  * row a pair can have), and the floats of scratch a call with that many splits needs: control words (a task counter and a

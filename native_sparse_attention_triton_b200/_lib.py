@@ -28,7 +28,7 @@ _SIGNATURES = {
     "nsa_compressed_attn_topk": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _F,
                                  _I, _P],
     "nsa_linear_compress_fwd": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _L, _L, _I, _P],
-    "nsa_pool_compress_fwd": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _L, _L, _I, _P],
+    "nsa_pool_compress_fwd": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _L, _L, _I, _P],
     "nsa_varlen_attn_bwd": [_P] * 12 + [_L] + [_I] * 11 + [_P, _F, _I, _P],
     "nsa_window_attn_bwd": [_P] * 11 + [_L] + [_I] * 7 + [_P, _F, _I, _P],
     "nsa_topk_sparse_attn_bwd": [_P] * 13 + [_L] + [_I] * 7 + [_P, _F, _I, _P],

@@ -14,6 +14,7 @@
 #include "dispatch.h"
 #include "host_util.h"
 #include "linear_fwd_tc.h"
+#include "pool_fwd_stream.h"
 #include "nsa_b200.h"
 
 namespace nsa {
@@ -249,7 +250,8 @@ static int launch_linear_fwd(LinFwdParams p, const void* pe, void* bias_scratch,
 }
 
 template <typename T, int D>
-static int launch_pool_fwd(PoolFwdParams p, const void* pe, void* bias_scratch, cudaStream_t stream) {
+static int launch_pool_fwd(PoolFwdParams p, const void* pe, void* bias_scratch, int total_len, int max_y_len, int dtype,
+                           cudaStream_t stream) {
   if (pe) {
     { LaunchScope ls_("pool_bias", stream); pool_bias_kernel<T><<<p.H, D, 0, stream>>>(static_cast<const T*>(pe), static_cast<const T*>(p.w),
                                                 static_cast<T*>(bias_scratch), p.ks, D); }
@@ -257,6 +259,9 @@ static int launch_pool_fwd(PoolFwdParams p, const void* pe, void* bias_scratch, 
   } else {
     p.bias = nullptr;
   }
+  if (pool_fwd_stream_eligible(p.H, D, p.M, p.ks, p.stride))
+    return pool_fwd_stream(p.x, p.w, p.bias, p.y, p.cu, p.ycu, p.B, total_len, p.M, max_y_len, p.H, D, p.ks, p.stride, p.x_sn, p.x_sh,
+                           dtype, stream);
   const long long total = (long long)p.M * p.H * (D / 8);
   const int blocks = (int)((total + 255) / 256);
   {
@@ -289,8 +294,8 @@ extern "C" int nsa_linear_compress_fwd(const void* x, const void* w, const void*
 }
 
 extern "C" int nsa_pool_compress_fwd(const void* x, const void* w, const void* pe, const int* cu_seqlens,
-                                     const int* y_cu_seqlens, void* y, void* bias_scratch, int batch, int total_y,
-                                     int num_heads, int head_dim, int kernel_size, int kernel_stride,
+                                     const int* y_cu_seqlens, void* y, void* bias_scratch, int total_len, int batch,
+                                     int total_y, int max_y_len, int num_heads, int head_dim, int kernel_size, int kernel_stride,
                                      long long x_stride_n, long long x_stride_h, int dtype, void* stream) {
   using namespace nsa;
   if (!x || !cu_seqlens || !y_cu_seqlens || batch <= 0 || num_heads <= 0) return kInvalid;
@@ -304,5 +309,6 @@ extern "C" int nsa_pool_compress_fwd(const void* x, const void* w, const void* p
   p.x = x; p.w = w; p.bias = nullptr; p.y = y; p.cu = cu_seqlens; p.ycu = y_cu_seqlens;
   p.x_sn = x_stride_n; p.x_sh = x_stride_h; p.B = batch; p.H = num_heads; p.D = head_dim; p.ks = kernel_size;
   p.stride = kernel_stride; p.M = total_y;
-  return NSA_DISPATCH_T_D(dtype, head_dim, launch_pool_fwd, p, pe, bias_scratch, static_cast<cudaStream_t>(stream));
+  return NSA_DISPATCH_T_D(dtype, head_dim, launch_pool_fwd, p, pe, bias_scratch, total_len, max_y_len, dtype,
+                          static_cast<cudaStream_t>(stream));
 }

@@ -103,7 +103,7 @@ def _compress_staged(cache: NSACache, batch: int, which: int, func: Callable, we
                                          x.stride(1), dtype_code(x), stream_ptr(x.device))
         _lib.check(rc, "nsa_linear_compress_fwd")
     else:
-        rc = lib.nsa_pool_compress_fwd(ptr(x), ptr(w), ptr(pec), ptr(cu), ptr(ycu), ptr(y), ptr(bias), batch, batch,
+        rc = lib.nsa_pool_compress_fwd(ptr(x), ptr(w), ptr(pec), ptr(cu), ptr(ycu), ptr(y), ptr(bias), x.shape[0], batch, batch, 1,
                                        cache.num_kv_heads, cache.head_dim, cache.kernel_size, cache.kernel_stride, x.stride(0),
                                        x.stride(1), dtype_code(x), stream_ptr(x.device))
         _lib.check(rc, "nsa_pool_compress_fwd")

@@ -61,7 +61,7 @@ class _Compress(torch.autograd.Function):
             _lib.check(rc, "nsa_linear_compress_fwd")
         else:
             rc = lib.nsa_pool_compress_fwd(ptr(x), ptr(wc), ptr(pec), ptr(cu_seqlens), ptr(y_cu), ptr(y), ptr(bias),
-                                           batch, total_y, num_heads, head_dim, kernel_size, kernel_stride,
+                                           x.shape[0], batch, total_y, max_y, num_heads, head_dim, kernel_size, kernel_stride,
                                            x.stride(0), x.stride(1), dtype_code(x), stream_ptr(x.device))
             _lib.check(rc, "nsa_pool_compress_fwd")
         ctx.save_for_backward(x, wc, pec, cu_seqlens, y_cu)

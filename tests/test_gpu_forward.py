@@ -1,5 +1,6 @@
 """Forward parity of the CUDA operators (through the C ABI) against the CPU oracle and the golden fixtures."""
 
+import numpy as np
 import pytest
 import torch
 
@@ -237,4 +238,37 @@ def test_linear_compress_many_waves_of_ctas(ops):
     y_ref, y_cu_ref = O.linear_compress(x.cuda().float(), w.cuda().float(), cu, ks, st, pe.cuda().float())
     assert torch.equal(y_cu.cpu(), y_cu_ref.cpu().to(torch.int32))
     close(y, y_ref, "linear_compress")
+    assert status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("H,seqlens,ks,st", [
+    (4, [150000, 33, 70007], 32, 16),    # 13 748 windows; a sequence without a window in the middle
+    (2, [140000], 32, 16),               # two heads per chunk, eight windows at a time
+    (3, [135001, 9000], 64, 16),         # three heads: the second head block is half empty; four chunks per window
+    (1, [70000, 70000], 16, 16),         # windows that do not overlap
+])
+def test_pool_compress_streaming_path(ops, dtype, H, seqlens, ks, st):
+    """Inputs of 8192 windows or more (head_dim 128) stream through shared memory in TMA chunks: weighted and average pooling,
+    with and without the position embedding, and on a view of x whose heads are sliced out of a wider tensor.  The oracle runs
+    on the GPU in fp32."""
+    d = 128
+    g = torch.Generator().manual_seed(200 + H + ks)
+    N = sum(seqlens)
+    x = torch.randn(N, H, d, generator=g).to(dtype).cuda()
+    wide = torch.randn(N, H + 2, d, generator=g).to(dtype).cuda()
+    wide[:, 1:H + 1] = x
+    w = (torch.rand(H, ks, generator=g) / ks).to(dtype).cuda()
+    pe = (torch.randn(H, ks, d, generator=g) * 0.02).to(dtype).cuda()
+    cu = torch.tensor([0] + list(np.cumsum(seqlens)), dtype=torch.int32).cuda()
+    for src, fn, ofn, wt, pos in ((x, ops.weightedpool_compress, O.weightedpool_compress, w, pe),
+                                  (wide[:, 1:H + 1], ops.weightedpool_compress, O.weightedpool_compress, w, None),
+                                  (x, ops.avgpool_compress, O.avgpool_compress, None, pe)):
+        y, y_cu = fn(src, wt, cu, ks, st, pos)
+        if wt is None:
+            y_ref, y_cu_ref = ofn(x.float(), None, cu, ks, st, pos.float() if pos is not None else None)
+        else:
+            y_ref, y_cu_ref = ofn(x.float(), wt.float(), cu, ks, st, pos.float() if pos is not None else None)
+        assert torch.equal(y_cu.cpu(), y_cu_ref.cpu().to(torch.int32))
+        close(y, y_ref, "pool_compress")
     assert status_ok()
