@@ -554,21 +554,34 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
   }
 }
 
-// fp32 accumulator -> storage type, rows of D contiguous elements with arbitrary row strides
+// fp32 accumulator -> storage type, rows of D contiguous elements with arbitrary row strides.  A thread converts
+// kConvertUnroll float4 pieces, 256 pieces apart, and issues all of its loads before the first store: one 16-byte load in
+// flight per thread left HBM two thirds busy.
+constexpr int kConvertUnroll = 4;
 template <typename T>
-__global__ void convert_rows_kernel(const float* __restrict__ src, void* dst, long long rows, int Hkv, int D, long long d_sn,
-                                    long long d_sh) {
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+__global__ void __launch_bounds__(256) convert_rows_kernel(const float* __restrict__ src, void* dst, long long rows, int Hkv, int D,
+                                                           long long d_sn, long long d_sh) {
   const int CH = D / 4;
-  if (idx >= rows * Hkv * CH) return;
-  const int c = idx % CH;
-  const int h = (idx / CH) % Hkv;
-  const long long n = idx / ((long long)CH * Hkv);
-  const float4 v = *reinterpret_cast<const float4*>(src + ((size_t)n * Hkv + h) * D + c * 4);
-  uint2 out;
-  out.x = DT<T>::pack(v.x, v.y);
-  out.y = DT<T>::pack(v.z, v.w);
-  *reinterpret_cast<uint2*>(static_cast<T*>(dst) + n * d_sn + (long long)h * d_sh + c * 4) = out;
+  const long long total = rows * Hkv * CH;
+  const long long base = (long long)blockIdx.x * (256 * kConvertUnroll) + threadIdx.x;
+  float4 v[kConvertUnroll];
+#pragma unroll
+  for (int u = 0; u < kConvertUnroll; ++u) {
+    const long long idx = base + u * 256;
+    v[u] = idx < total ? __ldcs(reinterpret_cast<const float4*>(src) + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll
+  for (int u = 0; u < kConvertUnroll; ++u) {
+    const long long idx = base + u * 256;
+    if (idx >= total) continue;
+    const int c = idx % CH;
+    const int h = (idx / CH) % Hkv;
+    const long long n = idx / ((long long)CH * Hkv);
+    uint2 out;
+    out.x = DT<T>::pack(v[u].x, v[u].y);
+    out.y = DT<T>::pack(v[u].z, v[u].w);
+    *reinterpret_cast<uint2*>(static_cast<T*>(dst) + n * d_sn + (long long)h * d_sh + c * 4) = out;
+  }
 }
 
 // (lse, delta) per (token, query head) for the backward passes: delta = sum_d o * dO in fp32.  16 lanes per row of
@@ -690,8 +703,8 @@ static int run_dense_bwd(const void* q, const void* k, const void* v, const void
   }
   if (rc) return rc;
   const long long n4 = (long long)total_k * Hkv * (D / 4);
-  { LaunchScope ls_("convert_dk", stream); convert_rows_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(dk32, dk, total_k, Hkv, D, S[12], S[13]); }
-  { LaunchScope ls_("convert_dv", stream); convert_rows_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(dv32, dv, total_k, Hkv, D, S[14], S[15]); }
+  { LaunchScope ls_("convert_dk", stream); convert_rows_kernel<T><<<(unsigned)((n4 + 256 * kConvertUnroll - 1) / (256 * kConvertUnroll)), 256, 0, stream>>>(dk32, dk, total_k, Hkv, D, S[12], S[13]); }
+  { LaunchScope ls_("convert_dv", stream); convert_rows_kernel<T><<<(unsigned)((n4 + 256 * kConvertUnroll - 1) / (256 * kConvertUnroll)), 256, 0, stream>>>(dv32, dv, total_k, Hkv, D, S[14], S[15]); }
   return cuda_rc(cudaGetLastError());
 }
 
@@ -821,11 +834,11 @@ static int run_sparse_bwd(const void* q, const void* k, const void* v, const voi
   if (fused) {
     const long long q4 = (long long)N * Hq * (D / 4);
     LaunchScope ls_("convert_dq", stream);
-    convert_rows_kernel<T><<<(unsigned)((q4 + 255) / 256), 256, 0, stream>>>(dq32, dq, N, Hq, D, S[10], S[11]);
+    convert_rows_kernel<T><<<(unsigned)((q4 + 256 * kConvertUnroll - 1) / (256 * kConvertUnroll)), 256, 0, stream>>>(dq32, dq, N, Hq, D, S[10], S[11]);
   }
   const long long n4 = (long long)N * Hkv * (D / 4);
-  { LaunchScope ls_("convert_dk", stream); convert_rows_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(dk32, dk, N, Hkv, D, S[12], S[13]); }
-  { LaunchScope ls_("convert_dv", stream); convert_rows_kernel<T><<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(dv32, dv, N, Hkv, D, S[14], S[15]); }
+  { LaunchScope ls_("convert_dk", stream); convert_rows_kernel<T><<<(unsigned)((n4 + 256 * kConvertUnroll - 1) / (256 * kConvertUnroll)), 256, 0, stream>>>(dk32, dk, N, Hkv, D, S[12], S[13]); }
+  { LaunchScope ls_("convert_dv", stream); convert_rows_kernel<T><<<(unsigned)((n4 + 256 * kConvertUnroll - 1) / (256 * kConvertUnroll)), 256, 0, stream>>>(dv32, dv, N, Hkv, D, S[14], S[15]); }
   return cuda_rc(cudaGetLastError());
 }
 
