@@ -237,9 +237,11 @@ static int launch_linear_fwd(LinFwdParams p, const void* pe, void* bias_scratch,
   } else {
     p.bias = nullptr;
   }
-  if (linear_fwd_tc_eligible(D, max_ylen, total_len, p.ks, p.stride))
-    return linear_fwd_tc(p.x, p.w, p.bias, p.y, p.cu, p.ycu, B, max_ylen, total_len, p.H, p.ks, p.stride, p.x_sn, p.x_sh, dtype,
-                         stream);
+  if (linear_fwd_tc_eligible(D, max_ylen, total_len, p.ks, p.stride)) {
+    const int rc = linear_fwd_tc(p.x, p.w, p.bias, p.y, p.cu, p.ycu, B, max_ylen, total_len, p.H, p.ks, p.stride, p.x_sn, p.x_sh,
+                                 dtype, stream);
+    if (rc != kInvalid && rc != kUnsupported) return rc;   // a view of x no tensor map describes: the gathering kernel below
+  }
   const size_t smem = 1024 + 2 * (64 * D * 2 + D * D * 2);
   auto kern = linear_fwd_kernel<T, D>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -259,9 +261,11 @@ static int launch_pool_fwd(PoolFwdParams p, const void* pe, void* bias_scratch, 
   } else {
     p.bias = nullptr;
   }
-  if (pool_fwd_stream_eligible(p.H, D, p.M, p.ks, p.stride))
-    return pool_fwd_stream(p.x, p.w, p.bias, p.y, p.cu, p.ycu, p.B, total_len, p.M, max_y_len, p.H, D, p.ks, p.stride, p.x_sn, p.x_sh,
-                           dtype, stream);
+  if (pool_fwd_stream_eligible(p.H, D, p.M, p.ks, p.stride)) {
+    const int rc = pool_fwd_stream(p.x, p.w, p.bias, p.y, p.cu, p.ycu, p.B, total_len, p.M, max_y_len, p.H, D, p.ks, p.stride,
+                                   p.x_sn, p.x_sh, dtype, stream);
+    if (rc != kInvalid && rc != kUnsupported) return rc;   // a view of x no tensor map describes: the per-thread kernel below
+  }
   const long long total = (long long)p.M * p.H * (D / 8);
   const int blocks = (int)((total + 255) / 256);
   {
