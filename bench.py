@@ -649,6 +649,34 @@ def compression_bandwidth(ops, dev):
             "avgpool_compress": (lambda: ops.avgpool_compress(x, None, cu, ks, st, pe), io, "pool_compress_fwd"),
             "linear_compress": (lambda: ops.linear_compress(x, wl, cu, ks, st, pe), io + 2 * (H * ks * d * d + H * ks * d), "linear_compress_fwd")}
     out = dict(tokens=N, heads=H)
+    # backward of the two pooling modes: dy and x read once, dx written once (average pooling needs no x)
+    dy = torch.randn(M, H, d, generator=g, device=dev).to(torch.bfloat16)
+    for t_ in (x, wp, pe):
+        t_.requires_grad_(True)
+    bwd = {"weightedpool_compress_bwd": (lambda: ops.weightedpool_compress(x, wp, cu, ks, st, pe)[0], 2 * (2 * N * H * d + M * H * d)),
+           "avgpool_compress_bwd": (lambda: ops.avgpool_compress(x, None, cu, ks, st, pe)[0], 2 * (N * H * d + M * H * d))}
+    for name, (fn, nbytes) in bwd.items():
+        for _ in range(2):
+            fn().backward(dy)
+            x.grad = wp.grad = pe.grad = None
+        reps, ms = 3, 0.0
+        for _ in range(reps):
+            y_ = fn()
+            flush.zero_()
+            pkg._lib.profile_collect()
+            pkg._lib.profile(True)
+            y_.backward(dy)
+            torch.cuda.synchronize()
+            kern = pkg._lib.profile_collect()
+            pkg._lib.profile(False)
+            x.grad = wp.grad = pe.grad = None
+            ms += sum(v_[1] for k_, v_ in kern.items() if k_.startswith("pool_dx"))
+        ms /= reps
+        out[name] = dict(kernels=sorted(k_ for k_ in kern if k_.startswith("pool_d")), main_kernel_ms=ms, algorithmic_bytes=nbytes,
+                         gb_per_s=nbytes / 1e9 / (ms / 1e3), frac_of_hbm_peak=nbytes / 1e9 / (ms / 1e3) / peaks()["hbm"],
+                         all_kernels_ms={k_: v_[1] for k_, v_ in kern.items()})
+    for t_ in (x, wp, pe):
+        t_.requires_grad_(False)
     with torch.no_grad():
         for name, (fn, nbytes, kern_name) in work.items():
             for _ in range(2):

@@ -224,11 +224,18 @@ int nsa_linear_compress_bwd(const void* x, const void* w, const void* pe, const 
 
 /* Backward of nsa_pool_compress_fwd: dx, dw [H, kernel_size] (iff w), dpe (iff pe).  Deterministic.
  * Replaces sliding_pool_dxdw_kernel + dw.sum(1) and the autograd of the bias,
- * native_sparse_attention/ops/triton/weighted_pool.py:88-179,241-298,320-324,357-362. */
+ * native_sparse_attention/ops/triton/weighted_pool.py:88-179,241-298,320-324,357-362.
+ *   workspace: fp32, nsa_pool_compress_bwd_workspace_floats(...) words: the column sums of dy ([H, d], needed iff pe) followed
+ *   by the partial rows of dw that the one-pass kernel for long inputs (131 072 tokens or more, head_dim 128, kernel_size
+ *   <= 32) leaves per (CTA, thread group); a workspace of only H * d words (or NULL without pe) is accepted and keeps long
+ *   inputs on the per-thread kernels.  max_seqlen is the longest input sequence. */
+long long nsa_pool_compress_bwd_workspace_floats(int total_len, int batch, int max_seqlen, int num_heads, int head_dim,
+                                                 int kernel_size, int kernel_stride);
 int nsa_pool_compress_bwd(const void* x, const void* w, const void* pe, const void* dy, const int* cu_seqlens,
-                          const int* y_cu_seqlens, void* dx, void* dw, void* dpe, float* dbias_scratch,
-                          int total_len, int batch, int total_y, int num_heads, int head_dim, int kernel_size,
-                          int kernel_stride, long long x_stride_n, long long x_stride_h, int dtype, void* stream);
+                          const int* y_cu_seqlens, void* dx, void* dw, void* dpe, float* workspace,
+                          long long workspace_floats, int total_len, int batch, int total_y, int max_seqlen,
+                          int num_heads, int head_dim, int kernel_size, int kernel_stride, long long x_stride_n,
+                          long long x_stride_h, int dtype, void* stream);
 
 /* Gated sum of the three branch outputs of an NSA layer,
  *   out[n, h, :] = gate[n, h, 0] * o_cmp[n, h, :] + gate[n, h, 1] * o_sel[n, h, :] + gate[n, h, 2] * o_win[n, h, :],

@@ -33,7 +33,7 @@ _SIGNATURES = {
     "nsa_window_attn_bwd": [_P] * 11 + [_L] + [_I] * 7 + [_P, _F, _I, _P],
     "nsa_topk_sparse_attn_bwd": [_P] * 13 + [_L] + [_I] * 7 + [_P, _F, _I, _P],
     "nsa_linear_compress_bwd": [_P] * 10 + [_I] * 8 + [_L, _L, _I, _P],
-    "nsa_pool_compress_bwd": [_P] * 10 + [_I] * 7 + [_L, _L, _I, _P],
+    "nsa_pool_compress_bwd": [_P] * 10 + [_L] + [_I] * 8 + [_L, _L, _I, _P],
     "nsa_gate_combine_fwd": [_P] * 5 + [_I, _I, _I, _P, _I, _P],
     "nsa_gate_combine_bwd": [_P] * 9 + [_I, _I, _I, _P, _I, _P],
     "nsa_rope": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _L, _L, _L, _L, _I, _P],
@@ -53,6 +53,7 @@ _SIGNATURES = {
 
 # functions that return a byte count (long long)
 _SIZE_QUERIES = {
+    "nsa_pool_compress_bwd_workspace_floats": [_I] * 7,
     "nsa_varlen_attn_bwd_workspace": [_I, _I, _I, _I, _I],
     "nsa_topk_sparse_attn_bwd_workspace": [_I, _I, _I, _I, _I, _I, _I],
     "nsa_launch_count": [],

@@ -15,6 +15,7 @@
 #include "dispatch.h"
 #include "host_util.h"
 #include "nsa_b200.h"
+#include "pool_bwd_stream.h"
 
 namespace nsa {
 
@@ -316,6 +317,32 @@ __global__ void __launch_bounds__(256) pool_dw_kernel(PoolBwdParams p) {
   }
 }
 
+// dw[h,k] from the streaming pass's partial rows (summed in slot order: deterministic) and dpe[h,k,:]
+template <typename T>
+__global__ void __launch_bounds__(256) pool_dw_finish_kernel(PoolBwdParams p, const float* __restrict__ partial, int nslots) {
+  __shared__ float red[8];
+  const int h = blockIdx.x, k = blockIdx.y;
+  float acc = 0.f;
+  for (int s = threadIdx.x; s < nslots; s += blockDim.x) acc += partial[((size_t)s * p.H + h) * p.ks + k];
+  if (p.pe)
+    for (int n = threadIdx.x; n < p.D; n += blockDim.x)
+      acc += DT<T>::to_float(static_cast<const T*>(p.pe)[((size_t)h * p.ks + k) * p.D + n]) * p.dbias[h * p.D + n];
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
+    static_cast<T*>(p.dw)[h * p.ks + k] = DT<T>::from_float(tot);
+  }
+  if (p.dpe) {
+    const float wv = DT<T>::to_float(static_cast<const T*>(p.w)[h * p.ks + k]);
+    for (int n = threadIdx.x; n < p.D; n += blockDim.x)
+      static_cast<T*>(p.dpe)[((size_t)h * p.ks + k) * p.D + n] = DT<T>::from_float(wv * p.dbias[h * p.D + n]);
+  }
+}
+
 template <typename T, int D>
 static int run_linear_bwd(LinBwdParams p, void* dpe, float* dbias, int total_y, int max_len, cudaStream_t stream) {
   if (p.pe) {
@@ -344,10 +371,29 @@ static int run_linear_bwd(LinBwdParams p, void* dpe, float* dbias, int total_y, 
 }
 
 template <typename T, int D>
-static int run_pool_bwd(PoolBwdParams p, float* dbias, int total_y, cudaStream_t stream) {
+static int run_pool_bwd(PoolBwdParams p, float* dbias, float* partial, long long partial_floats, int total_y, int max_seqlen,
+                        int dtype, cudaStream_t stream) {
   if (p.pe) {
     { LaunchScope ls_("colsum", stream); colsum_kernel<T><<<dim3(p.H, D / 8), 256, 0, stream>>>(static_cast<const T*>(p.dy), dbias, total_y, p.H, D); }
     p.dbias = dbias;
+  }
+  // long inputs: one streaming pass writes dx and (weighted pooling) the partial rows of dw
+  const long long need = pool_bwd_stream_partial_floats(p.H, D, p.N, p.B, max_seqlen, p.ks, p.stride);
+  if (total_y > 0 && need > 0 && (!p.dw || (partial && partial_floats >= need))) {
+    int nslots = 0;
+    const int rc = pool_bwd_stream(p.x, p.dw ? p.w : nullptr, p.dy, p.dx, p.dw ? partial : nullptr, &nslots, p.cu, p.ycu, p.B, p.N,
+                                   max_seqlen, p.H, D, p.ks, p.stride, p.x_sn, p.x_sh, dtype, stream);
+    if (rc != kInvalid && rc != kUnsupported) {
+      if (rc) return rc;
+      if (p.dw) {
+        LaunchScope ls_("pool_dw_finish", stream);
+        pool_dw_finish_kernel<T><<<dim3(p.H, p.ks), 256, 0, stream>>>(p, partial, nslots);
+      } else if (p.dpe) {
+        LaunchScope ls_("pool_dw", stream);
+        pool_dw_kernel<T><<<dim3(p.H, p.ks), 256, 0, stream>>>(p);   // average pooling: only dpe is written
+      }
+      return cuda_rc(cudaGetLastError());
+    }
   }
   const long long total = (long long)p.N * p.H * (D / 8);
   { LaunchScope ls_("pool_dx", stream); pool_dx_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(p); }
@@ -375,12 +421,26 @@ extern "C" int nsa_linear_compress_bwd(const void* x, const void* w, const void*
                           static_cast<cudaStream_t>(stream));
 }
 
+extern "C" long long nsa_pool_compress_bwd_workspace_floats(int total_len, int batch, int max_seqlen, int num_heads, int head_dim,
+                                                           int kernel_size, int kernel_stride) {
+  if (total_len <= 0 || batch <= 0 || num_heads <= 0 || head_dim <= 0 || kernel_size <= 0 || kernel_stride <= 0) return 0;
+  return (long long)num_heads * head_dim +
+         nsa::pool_bwd_stream_partial_floats(num_heads, head_dim, total_len, batch, max_seqlen, kernel_size, kernel_stride);
+}
+
 extern "C" int nsa_pool_compress_bwd(const void* x, const void* w, const void* pe, const void* dy, const int* cu_seqlens,
-                                     const int* y_cu_seqlens, void* dx, void* dw, void* dpe, float* dbias_scratch,
-                                     int total_len, int batch, int total_y, int num_heads, int head_dim, int kernel_size,
-                                     int kernel_stride, long long x_stride_n, long long x_stride_h, int dtype, void* stream) {
+                                     const int* y_cu_seqlens, void* dx, void* dw, void* dpe, float* workspace,
+                                     long long workspace_floats, int total_len, int batch, int total_y, int max_seqlen,
+                                     int num_heads, int head_dim, int kernel_size, int kernel_stride, long long x_stride_n,
+                                     long long x_stride_h, int dtype, void* stream) {
   using namespace nsa;
-  if (!x || !cu_seqlens || !y_cu_seqlens || !dx || batch <= 0 || num_heads <= 0 || total_len <= 0) return kInvalid;
+  if (!x || !cu_seqlens || !y_cu_seqlens || !dx || batch <= 0 || num_heads <= 0 || total_len <= 0 || max_seqlen <= 0) return kInvalid;
+  // workspace: [H, d] column sums of dy (needed iff pe), then the partial rows of dw of the streaming pass (optional: without
+  // them long inputs run on the per-thread kernels)
+  const long long dbias_floats = (long long)num_heads * head_dim;
+  float* dbias_scratch = workspace && workspace_floats >= dbias_floats ? workspace : nullptr;
+  float* partial = workspace && workspace_floats > dbias_floats ? workspace + dbias_floats : nullptr;
+  const long long partial_floats = partial ? workspace_floats - dbias_floats : 0;
   if (pe && (!dpe || !dbias_scratch)) return kInvalid;
   if (w && !dw) return kInvalid;
   if (kernel_size <= 0 || kernel_stride <= 0 || kernel_size % kernel_stride) return kInvalid;
@@ -390,5 +450,6 @@ extern "C" int nsa_pool_compress_bwd(const void* x, const void* w, const void* p
   p.x = x; p.w = w; p.pe = pe; p.dy = dy; p.dbias = nullptr; p.dx = dx; p.dw = w ? dw : nullptr; p.dpe = pe ? dpe : nullptr;
   p.cu = cu_seqlens; p.ycu = y_cu_seqlens; p.x_sn = x_stride_n; p.x_sh = x_stride_h;
   p.N = total_len; p.B = batch; p.H = num_heads; p.D = head_dim; p.ks = kernel_size; p.stride = kernel_stride;
-  return NSA_DISPATCH_T_D(dtype, head_dim, run_pool_bwd, p, dbias_scratch, total_y, static_cast<cudaStream_t>(stream));
+  return NSA_DISPATCH_T_D(dtype, head_dim, run_pool_bwd, p, dbias_scratch, partial, partial_floats, total_y, max_seqlen, dtype,
+                          static_cast<cudaStream_t>(stream));
 }

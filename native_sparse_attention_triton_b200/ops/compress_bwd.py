@@ -24,9 +24,12 @@ def compress_backward(ctx, dy):
         _lib.check(rc, "nsa_linear_compress_bwd")
     else:
         dw = torch.empty_like(w) if w is not None else None
+        n_ws = lib.nsa_pool_compress_bwd_workspace_floats(total_len, batch, max_len, num_heads, head_dim, kernel_size, kernel_stride)
+        ws = torch.empty(n_ws, dtype=torch.float32, device=x.device)   # column sums of dy, then the partial rows of dw
         rc = lib.nsa_pool_compress_bwd(ptr(x), ptr(w), ptr(pe), ptr(dy), ptr(cu_seqlens), ptr(y_cu), ptr(dx), ptr(dw),
-                                       ptr(dpe), ptr(dbias), total_len, batch, total_y, num_heads, head_dim, kernel_size,
-                                       kernel_stride, x.stride(0), x.stride(1), dtype_code(x), stream_ptr(x.device))
+                                       ptr(dpe), ptr(ws), n_ws, total_len, batch, total_y, max_len, num_heads, head_dim,
+                                       kernel_size, kernel_stride, x.stride(0), x.stride(1), dtype_code(x),
+                                       stream_ptr(x.device))
         _lib.check(rc, "nsa_pool_compress_bwd")
     # gradients for (x, w, pe, cu_seqlens, kernel_size, kernel_stride, mode)
     return dx, dw, dpe, None, None, None, None

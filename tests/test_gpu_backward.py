@@ -1,4 +1,5 @@
 """Backward parity of the trainable operators against autograd over the fp32 CPU oracle."""
+import numpy as np
 import pytest
 import torch
 
@@ -165,4 +166,43 @@ def test_chain_backward_cfg_like(ops):
     # cannot see, so its exact gradient is zero and only rounding noise remains (test_compress_backward covers dpe)
     for n in names[:-1]:
         close(t[n].grad, r[n].grad, "d" + n, chain=True)
+    assert status_ok()
+
+
+@pytest.mark.parametrize("H,seqlens,ks,st", [
+    (4, [100000, 20, 45003, 31], 32, 16),   # sequences without a window (their dx is zero), a ragged tail
+    (2, [140000], 32, 16),
+    (3, [120001, 15000], 16, 16),           # three heads (half-empty second head block); windows that do not overlap
+    (4, [135000], 32, 8),                   # stride 8: four windows over every token
+])
+@pytest.mark.parametrize("mode", ["weighted", "avg"])
+def test_pool_compress_backward_streaming_path(ops, H, seqlens, ks, st, mode):
+    """Inputs of 131 072 tokens or more (head_dim 128, kernel <= 32) take the one-pass backward: dx written once, x and dy
+    read once, dw from per-(CTA, group) partial rows added in a fixed order.  Against autograd through the oracle, run on the
+    GPU in fp32; dw is a sum over ~10^7 products, compared relative to its own size."""
+    d = 128
+    g = torch.Generator().manual_seed(300 + H + ks + st)
+    N = sum(seqlens)
+    cu = torch.tensor([0] + list(np.cumsum(seqlens)), dtype=torch.int32).cuda()
+    xb = torch.randn(N, H, d, generator=g).bfloat16()
+    wb = (torch.rand(H, ks, generator=g) / ks).bfloat16()
+    peb = (torch.randn(H, ks, d, generator=g) * 0.02).bfloat16()
+    x, pe = xb.cuda().requires_grad_(True), peb.cuda().requires_grad_(True)
+    w = wb.cuda().requires_grad_(True) if mode == "weighted" else None
+    fn = ops.weightedpool_compress if mode == "weighted" else ops.avgpool_compress
+    y, _ = fn(x, w, cu, ks, st, pe)
+    dy = torch.randn(y.shape, generator=g).bfloat16().cuda()
+    y.backward(dy)
+    xr, per = xb.cuda().float().requires_grad_(True), peb.cuda().float().requires_grad_(True)
+    wr = wb.cuda().float().requires_grad_(True) if mode == "weighted" else None
+    ofn = O.weightedpool_compress if mode == "weighted" else O.avgpool_compress
+    yr, _ = ofn(xr, wr, cu, ks, st, per)
+    yr.backward(dy.float())
+    close(x.grad, xr.grad, "dx")
+    # tokens no window covers (sequences shorter than the kernel, ragged tails) get exact zeros
+    assert float(x.grad[xr.grad == 0].float().abs().max()) == 0.0
+    close(pe.grad, per.grad, "dpe")
+    if mode == "weighted":
+        rel = (w.grad.float() - wr.grad).abs().max() / wr.grad.abs().max()
+        assert float(rel) <= 1e-2, float(rel)
     assert status_ok()
