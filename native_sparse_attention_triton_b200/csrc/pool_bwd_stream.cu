@@ -153,9 +153,13 @@ __global__ void __launch_bounds__(kPbConsumers + 32, 1) pool_bwd_stream_kernel(c
   const int row_bytes = p.hb * p.D * 2;
   T* dxp = static_cast<T*>(p.dx) + ((size_t)s0 * p.H + hq) * p.D + cc * 8;
 
+  float2 dynext[4];   // the next chunk's new gradient row, fetched one chunk ahead
+  load_dy(c0 + cg0, dynext);
   for (int i = 0; i < cg1 - cg0; ++i) {
     const int c = c0 + cg0 + i;
-    load_dy(c, dyr[0]);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) dyr[0][e] = dynext[e];
+    load_dy(i + 1 < cg1 - cg0 ? c + 1 : -1, dynext);
     const uint8_t* rows = nullptr;
     if (DW) {
       const int s = i % p.slots;
