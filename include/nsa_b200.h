@@ -96,6 +96,22 @@ int nsa_pool_compress_fwd(const void* x, const void* w, const void* pe, const in
                           int total_y, int max_y_len, int num_heads, int head_dim, int kernel_size,
                           int kernel_stride, long long x_stride_n, long long x_stride_h, int dtype, void* stream);
 
+/* The compression of a decode step for both pooling modes, K and V in one launch: every sequence contributes exactly
+ * one window, the kernel_size rows of its staging buffer (x_k, x_v: [batch, kernel_size, H, d] views with strides
+ * x_stride_b, x_stride_n, x_stride_h), so no cu_seqlens is read.  w_k / w_v [H, kernel_size] or NULL (average); bias_k /
+ * bias_v [H, d] (the position embedding folded through the weights by nsa_pool_bias, which does not change between steps)
+ * or NULL; y_k, y_v [batch, H, d] contiguous.  Replaces the two compress_func calls on the staging buffers in
+ * native_sparse_attention/infer/inference_func.py:56-87 when both are pooling operators. */
+int nsa_pool_compress_decode_pair(const void* x_k, const void* x_v, const void* w_k, const void* w_v, const void* bias_k,
+                                  const void* bias_v, void* y_k, void* y_v, int batch, int num_heads, int head_dim,
+                                  int kernel_size, long long x_stride_b, long long x_stride_n, long long x_stride_h,
+                                  int dtype, void* stream);
+
+/* bias[h, :] = sum_k w[h, k] * pe[h, k, :] (w == NULL: the mean over k), in the storage type: the term the pooling
+ * operators add to every compressed row (native_sparse_attention/ops/triton/weighted_pool.py:301-363). */
+int nsa_pool_bias(const void* pe, const void* w, void* bias, int num_heads, int head_dim, int kernel_size, int dtype,
+                  void* stream);
+
 /* Number of split-KV partitions the decode kernels want for this problem (>= 1; max_tiles = 64-key tiles of the longest
  * row a pair can have), and the floats of scratch a call with that many splits needs: control words (a task counter and a
  * per-(sequence, KV head) counter at the FRONT of the scratch: batch*num_kv_heads + 1 ints), the splits' partial results

@@ -42,6 +42,8 @@ _SIGNATURES = {
     "nsa_kv_cache_fill": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "nsa_kv_cache_stage_decode": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "nsa_kv_cache_append_decode": [_P] * 13 + [_I] * 7 + [_P, _P],
+    "nsa_pool_compress_decode_pair": [_P] * 8 + [_I, _I, _I, _I, _L, _L, _L, _I, _P],
+    "nsa_pool_bias": [_P, _P, _P, _I, _I, _I, _I, _P],
     "nsa_decode_num_splits": [_I, _I, _I],
     "nsa_flash_attn_decode": [_P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P, _F, _I, _P],
     "nsa_flash_attn_decode_static": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _F, _I, _P],

@@ -227,6 +227,89 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(PoolFwdParams p) {
   *reinterpret_cast<uint4*>(static_cast<T*>(p.y) + ((size_t)mg * p.H + h) * p.D + c * 8) = out;
 }
 
+// ------------------------------------------------------------------------------------------------
+// pooling of the staged rows of a decode step: K and V in one launch
+// ------------------------------------------------------------------------------------------------
+// Each sequence contributes exactly one window: the kernel_size rows of its staging buffer.  No cu_seqlens, no sequence
+// search: the only loads are the rows, the weights and the bias, all independent of each other (one memory round trip; with
+// cold caches the general kernel's chain of dependent loads costs 10 us per launch).
+struct PoolPairParams {
+  const void* x[2];     // [B, ks, H, D] views (strides x_sb, x_sn, x_sh)
+  const void* w[2];     // [H, ks] or nullptr (average)
+  const void* bias[2];  // [H, D] or nullptr
+  void* y[2];           // [B, H, D] contiguous
+  long long x_sb, x_sn, x_sh;
+  int B, H, D, ks;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) pool_decode_pair_kernel(PoolPairParams p) {
+  const int which = blockIdx.y;
+  const int CH = p.D / 8;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= p.B * p.H * CH) return;
+  const int c = idx % CH;
+  const int h = (idx / CH) % p.H;
+  const int b = idx / (CH * p.H);
+  const T* x = static_cast<const T*>(p.x[which]) + (long long)b * p.x_sb + (long long)h * p.x_sh + c * 8;
+  const T* w = p.w[which] ? static_cast<const T*>(p.w[which]) + h * p.ks : nullptr;
+  uint4 bv = make_uint4(0u, 0u, 0u, 0u);
+  if (p.bias[which]) bv = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.bias[which]) + (size_t)h * p.D + c * 8));
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int k0 = 0; k0 < p.ks; k0 += 16) {
+    uint4 v[16];
+    float wv[16];
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      v[u] = __ldg(reinterpret_cast<const uint4*>(x + (long long)(k0 + u) * p.x_sn));
+      wv[u] = w ? DT<T>::to_float(w[k0 + u]) : 1.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      const uint32_t uu[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = DT<T>::unpack(uu[e]);
+        acc[2 * e] += wv[u] * f.x;
+        acc[2 * e + 1] += wv[u] * f.y;
+      }
+    }
+  }
+  if (!w) {
+    const float inv = 1.f / (float)p.ks;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] *= inv;
+  }
+  if (p.bias[which]) {
+    const uint32_t bu[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = DT<T>::unpack(bu[e]);
+      acc[2 * e] = DT<T>::to_float(DT<T>::from_float(acc[2 * e])) + f.x;
+      acc[2 * e + 1] = DT<T>::to_float(DT<T>::from_float(acc[2 * e + 1])) + f.y;
+    }
+  }
+  uint4 out;
+  out.x = DT<T>::pack(acc[0], acc[1]);
+  out.y = DT<T>::pack(acc[2], acc[3]);
+  out.z = DT<T>::pack(acc[4], acc[5]);
+  out.w = DT<T>::pack(acc[6], acc[7]);
+  *reinterpret_cast<uint4*>(static_cast<T*>(p.y[which]) + ((size_t)b * p.H + h) * p.D + c * 8) = out;
+}
+
+template <typename T, int D>
+static int launch_pool_decode_pair(PoolPairParams p, cudaStream_t stream) {
+  const int total = p.B * p.H * (D / 8);
+  { LaunchScope ls_("pool_compress_decode", stream); pool_decode_pair_kernel<T><<<dim3((total + 255) / 256, 2), 256, 0, stream>>>(p); }
+  return cuda_rc(cudaGetLastError());
+}
+
+template <typename T, int D>
+static int launch_pool_bias(const void* pe, const void* w, void* bias, int H, int ks, cudaStream_t stream) {
+  { LaunchScope ls_("pool_bias", stream); pool_bias_kernel<T><<<H, D, 0, stream>>>(static_cast<const T*>(pe), static_cast<const T*>(w), static_cast<T*>(bias), ks, D); }
+  return cuda_rc(cudaGetLastError());
+}
+
 template <typename T, int D>
 static int launch_linear_fwd(LinFwdParams p, const void* pe, void* bias_scratch, int B, int max_ylen, int total_len, int dtype,
                              cudaStream_t stream) {
@@ -315,4 +398,26 @@ extern "C" int nsa_pool_compress_fwd(const void* x, const void* w, const void* p
   p.stride = kernel_stride; p.M = total_y;
   return NSA_DISPATCH_T_D(dtype, head_dim, launch_pool_fwd, p, pe, bias_scratch, total_len, max_y_len, dtype,
                           static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nsa_pool_bias(const void* pe, const void* w, void* bias, int num_heads, int head_dim, int kernel_size, int dtype,
+                             void* stream) {
+  using namespace nsa;
+  if (!pe || !bias || num_heads <= 0 || kernel_size <= 0) return kInvalid;
+  return NSA_DISPATCH_T_D(dtype, head_dim, launch_pool_bias, pe, w, bias, num_heads, kernel_size, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nsa_pool_compress_decode_pair(const void* x_k, const void* x_v, const void* w_k, const void* w_v, const void* bias_k,
+                                             const void* bias_v, void* y_k, void* y_v, int batch, int num_heads, int head_dim,
+                                             int kernel_size, long long x_stride_b, long long x_stride_n, long long x_stride_h,
+                                             int dtype, void* stream) {
+  using namespace nsa;
+  if (!x_k || !x_v || !y_k || !y_v || batch <= 0 || num_heads <= 0 || kernel_size <= 0) return kInvalid;
+  if (kernel_size % 16) return kUnsupported;
+  if ((x_stride_b | x_stride_n | x_stride_h) % 8 || !aligned16(x_k) || !aligned16(x_v) || !aligned16(y_k) || !aligned16(y_v)) return kInvalid;
+  if ((bias_k && !aligned16(bias_k)) || (bias_v && !aligned16(bias_v))) return kInvalid;
+  PoolPairParams p;
+  p.x[0] = x_k; p.x[1] = x_v; p.w[0] = w_k; p.w[1] = w_v; p.bias[0] = bias_k; p.bias[1] = bias_v; p.y[0] = y_k; p.y[1] = y_v;
+  p.x_sb = x_stride_b; p.x_sn = x_stride_n; p.x_sh = x_stride_h; p.B = batch; p.H = num_heads; p.D = head_dim; p.ks = kernel_size;
+  return NSA_DISPATCH_T_D(dtype, head_dim, launch_pool_decode_pair, p, static_cast<cudaStream_t>(stream));
 }

@@ -110,6 +110,51 @@ def _compress_staged(cache: NSACache, batch: int, which: int, func: Callable, we
     return y
 
 
+_pool_bias_cache = {}   # (id(w), id(pe)) -> (weakref w, weakref pe, versions, bias tensor)
+
+
+def _pool_bias(weight, pe):
+    """The position embedding folded through the pooling weights, [H, d]: it changes only when the parameters do, so it is
+    computed once per (weight, pe) pair and version, not once per decode step."""
+    import weakref
+
+    key = (id(weight), id(pe))
+    versions = (weight._version if weight is not None else -1, pe._version)
+    hit = _pool_bias_cache.get(key)
+    if hit is not None and hit[0]() is weight and hit[1]() is pe and hit[2] == versions:
+        return hit[3]
+    bias = torch.empty(pe.shape[0], pe.shape[2], dtype=pe.dtype, device=pe.device)
+    w = weight.contiguous() if weight is not None else None
+    rc = _lib.lib().nsa_pool_bias(ptr(pe.contiguous()), ptr(w), ptr(bias), pe.shape[0], pe.shape[2], pe.shape[1], dtype_code(pe),
+                                  stream_ptr(pe.device))
+    _lib.check(rc, "nsa_pool_bias")
+    if len(_pool_bias_cache) > 256:
+        _pool_bias_cache.clear()
+    _pool_bias_cache[key] = (weakref.ref(weight) if weight is not None else (lambda: None), weakref.ref(pe), versions, bias)
+    return bias
+
+
+_POOL_FUNCS = (ops.weightedpool_compress, ops.avgpool_compress)
+
+
+def _compress_staged_pair(cache: NSACache, batch: int, funcs, weights, pe):
+    """Both staging buffers pooled in one launch (nsa_pool_compress_decode_pair): one compressed key row and one compressed
+    value row per sequence; the key's position-embedding bias comes from the cache above."""
+    stage = cache.before_compress_kv_cache
+    xk, xv = stage[0, :batch], stage[1, :batch]            # [batch, kernel_size, H, d]
+    wk = weights[0].contiguous() if funcs[0] is ops.weightedpool_compress else None
+    wv = weights[1].contiguous() if funcs[1] is ops.weightedpool_compress else None
+    bias_k = _pool_bias(wk, pe) if pe is not None else None
+    yk = torch.empty(batch, cache.num_kv_heads, cache.head_dim, dtype=stage.dtype, device=stage.device)
+    yv = torch.empty_like(yk)
+    torch.cuda.set_device(stage.device)
+    rc = _lib.lib().nsa_pool_compress_decode_pair(ptr(xk), ptr(xv), ptr(wk), ptr(wv), ptr(bias_k), None, ptr(yk), ptr(yv), batch,
+                                                  cache.num_kv_heads, cache.head_dim, cache.kernel_size, xk.stride(0), xk.stride(1),
+                                                  xk.stride(2), dtype_code(stage), stream_ptr(stage.device))
+    _lib.check(rc, "nsa_pool_compress_decode_pair")
+    return yk, yv
+
+
 @torch.no_grad()
 def nsa_infer(cu_seqlens: torch.Tensor, step: int, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
               gate_value: torch.Tensor, rope, cache: NSACache, compress_weight: Tuple[torch.Tensor, torch.Tensor],
@@ -143,8 +188,11 @@ def nsa_infer(cu_seqlens: torch.Tensor, step: int, query: torch.Tensor, key: tor
 
     # ---- decode: nothing below reads a device value on the host ----
     cache.prepare_compress(cu_seqlens, step, key, value)
-    compress_key = _compress_staged(cache, batch, 0, compress_func[0], compress_weight[0], intra_block_pe)
-    compress_value = _compress_staged(cache, batch, 1, compress_func[1], compress_weight[1], None)
+    if compress_func[0] in _POOL_FUNCS and compress_func[1] in _POOL_FUNCS:
+        compress_key, compress_value = _compress_staged_pair(cache, batch, compress_func, compress_weight, intra_block_pe)
+    else:
+        compress_key = _compress_staged(cache, batch, 0, compress_func[0], compress_weight[0], intra_block_pe)
+        compress_value = _compress_staged(cache, batch, 1, compress_func[1], compress_weight[1], None)
     fast_rope = rope if hasattr(rope, "decode_at3") else _device_rope_of(rope)
     if fast_rope is not None:
         # the new token's index is the number of tokens cached so far; the compressed token's, the compressed count
