@@ -259,6 +259,7 @@ struct IndexParams {
   int* cursor;           // [bins]
   int* offsets;          // [bins + 1] exclusive scan of count
   int* item_base;        // [bins + 1] exclusive scan of ceil(count / chunk)
+  int* item_bin;         // [items] the bin of every work item (so that a CTA finds its bin with one load, not a search)
   int* list;             // [capacity] global token ids
   long long t_sh, t_sn, t_sk;
   int N, B, Hkv, T, block_size, TB, chunk;
@@ -317,7 +318,9 @@ __global__ void index_scan_kernel(IndexParams p) {
     }
     if (i < total) {
       p.offsets[i] = carry_cnt + s_cnt[threadIdx.x] - c;
-      p.item_base[i] = carry_itm + s_itm[threadIdx.x] - it;
+      const int first = carry_itm + s_itm[threadIdx.x] - it;
+      p.item_base[i] = first;
+      for (int k2 = 0; k2 < it; ++k2) p.item_bin[first + k2] = i;
     }
     __syncthreads();
     if (threadIdx.x == 1023) { carry_cnt += s_cnt[1023]; carry_itm += s_itm[1023]; }
@@ -359,12 +362,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     const int item = blockIdx.x;
     const int total_x = p.Hkv * p.NW * p.TB;
     if (item >= __ldg(p.item_base + total_x)) return;
-    int lo = 0, hi = total_x;  // item_base[lo] <= item < item_base[hi]
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (__ldg(p.item_base + mid) <= item) lo = mid; else hi = mid;
-    }
-    const int x = lo;
+    const int x = __ldg(p.item_bin + item);  // item_base[x] <= item < item_base[x + 1]
     h = x / (p.NW * p.TB);
     const int gb = x % p.TB;
     const int b = find_sequence(p.cu_blocks, p.B, gb);
@@ -686,7 +684,7 @@ static int run_dense_bwd(const void* q, const void* k, const void* v, const void
   }
   DkdvParams d;
   d.ld = ld; d.dk32 = dk32; d.dv32 = dv32; d.cu_q = cu_q; d.cu_k = cu_k;
-  d.cu_blocks = nullptr; d.offsets = nullptr; d.item_base = nullptr; d.list = nullptr;
+  d.cu_blocks = nullptr; d.offsets = nullptr; d.item_base = nullptr; d.item_bin = nullptr; d.list = nullptr;
   d.B = batch; d.Hq = Hq; d.Hkv = Hkv; d.G = G; d.TB = 0; d.NW = 1; d.block_size = kKeyTile;
   int chunk = 256;
   while (chunk < 1024 && chunk * 16 < max_q) chunk <<= 1;
@@ -727,6 +725,7 @@ static size_t sparse_ws_bytes(int N, int batch, int Hq, int Hkv, int D, int topk
   const size_t x = (size_t)Hkv * sparse_windows(N, Hq / Hkv, D).second * TB + 1;
   return align_up((size_t)N * Hq * sizeof(float2), 256) + 2 * align_up((size_t)N * Hkv * D * sizeof(float), 256) +
          4 * align_up(x * sizeof(int), 256) + align_up((size_t)Hkv * N * topk * sizeof(int), 256) +
+         align_up(((size_t)Hkv * N * topk / kSparseChunk + x) * sizeof(int), 256) +
          (sparse_fused_dq(Hq / Hkv, D) ? align_up((size_t)N * Hq * D * sizeof(float), 256) : 0);
 }
 
@@ -757,6 +756,8 @@ static int run_sparse_bwd(const void* q, const void* k, const void* v, const voi
   w += align_up(X * sizeof(int), 256);
   int* list = reinterpret_cast<int*>(w);
   w += align_up((size_t)Hkv * N * topk * sizeof(int), 256);
+  int* item_bin = reinterpret_cast<int*>(w);   // one entry per possible work item (the grid's upper bound below)
+  w += align_up(((size_t)Hkv * N * topk / kSparseChunk + X) * sizeof(int), 256);
   const bool fused = sparse_fused_dq(G, D);  // dQ comes out of the tcgen05 dK/dV pass; otherwise the per-token dQ kernel runs
   float* dq32 = fused ? reinterpret_cast<float*>(w) : nullptr;
   // dk32, dv32, count, cursor are contiguous: one memset
@@ -777,7 +778,7 @@ static int run_sparse_bwd(const void* q, const void* k, const void* v, const voi
 
   IndexParams ip;
   ip.topk_idx = topk_idx; ip.cu_seqlens = cu; ip.cu_blocks = cu_blocks; ip.count = count; ip.cursor = cursor;
-  ip.offsets = offsets; ip.item_base = item_base; ip.list = list;
+  ip.offsets = offsets; ip.item_base = item_base; ip.item_bin = item_bin; ip.list = list;
   ip.t_sh = S[16]; ip.t_sn = S[17]; ip.t_sk = S[18];
   ip.N = N; ip.B = batch; ip.Hkv = Hkv; ip.T = topk; ip.block_size = block_size; ip.TB = TB; ip.chunk = kSparseChunk; ip.W = W; ip.NW = NW;
   ip.capacity = (long long)Hkv * N * topk;
@@ -815,7 +816,7 @@ static int run_sparse_bwd(const void* q, const void* k, const void* v, const voi
   }
   DkdvParams d;
   d.ld = ld; d.dk32 = dk32; d.dv32 = dv32; d.dq32 = dq32; d.cu_q = cu; d.cu_k = cu;
-  d.cu_blocks = cu_blocks; d.offsets = offsets; d.item_base = item_base; d.list = list;
+  d.cu_blocks = cu_blocks; d.offsets = offsets; d.item_base = item_base; d.item_bin = item_bin; d.list = list;
   d.B = batch; d.Hq = Hq; d.Hkv = Hkv; d.G = G; d.TB = TB; d.NW = NW; d.chunk = kSparseChunk; d.block_size = block_size;
   d.window = 1; d.stride = 1; d.causal = 1; d.left = -1;
   d.scale2 = p.scale2; d.sm_scale = sm_scale; d.st = p.st;

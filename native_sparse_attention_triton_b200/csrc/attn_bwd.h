@@ -18,6 +18,7 @@ struct DkdvParams {
   const int* cu_blocks;
   const int* offsets;
   const int* item_base;
+  const int* item_bin;   // [items] bin of every work item
   const int* list;
   int B, Hq, Hkv, G, TB, chunk, block_size;
   int NW;  // sparse: token windows per KV head; bin x = (head * NW + window) * TB + block
