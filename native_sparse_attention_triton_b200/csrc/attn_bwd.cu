@@ -684,7 +684,7 @@ static int run_dense_bwd(const void* q, const void* k, const void* v, const void
   }
   DkdvParams d;
   d.ld = ld; d.dk32 = dk32; d.dv32 = dv32; d.cu_q = cu_q; d.cu_k = cu_k;
-  d.cu_blocks = nullptr; d.offsets = nullptr; d.item_base = nullptr; d.item_bin = nullptr; d.list = nullptr;
+  d.cu_blocks = nullptr; d.offsets = nullptr; d.item_base = nullptr; d.item_bin = nullptr; d.item_counter = nullptr; d.list = nullptr;
   d.B = batch; d.Hq = Hq; d.Hkv = Hkv; d.G = G; d.TB = 0; d.NW = 1; d.block_size = kKeyTile;
   int chunk = 256;
   while (chunk < 1024 && chunk * 16 < max_q) chunk <<= 1;
@@ -817,6 +817,7 @@ static int run_sparse_bwd(const void* q, const void* k, const void* v, const voi
   DkdvParams d;
   d.ld = ld; d.dk32 = dk32; d.dv32 = dv32; d.dq32 = dq32; d.cu_q = cu; d.cu_k = cu;
   d.cu_blocks = cu_blocks; d.offsets = offsets; d.item_base = item_base; d.item_bin = item_bin; d.list = list;
+  d.item_counter = cursor + (X - 1);   // the spare last word of the zeroed cursor array
   d.B = batch; d.Hq = Hq; d.Hkv = Hkv; d.G = G; d.TB = TB; d.NW = NW; d.chunk = kSparseChunk; d.block_size = block_size;
   d.window = 1; d.stride = 1; d.causal = 1; d.left = -1;
   d.scale2 = p.scale2; d.sm_scale = sm_scale; d.st = p.st;

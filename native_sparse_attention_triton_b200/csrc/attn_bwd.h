@@ -19,6 +19,7 @@ struct DkdvParams {
   const int* offsets;
   const int* item_base;
   const int* item_bin;   // [items] bin of every work item
+  int* item_counter;     // zero at launch: the persistent tcgen05 pass hands out items from it
   const int* list;
   int B, Hq, Hkv, G, TB, chunk, block_size;
   int NW;  // sparse: token windows per KV head; bin x = (head * NW + window) * TB + block
