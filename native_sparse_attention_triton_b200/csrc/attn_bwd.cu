@@ -294,36 +294,48 @@ __global__ void index_scatter_kernel(IndexParams p) {
   }
 }
 
-// single CTA: exclusive scans of count and of the per-block chunk count
-__global__ void index_scan_kernel(IndexParams p) {
-  __shared__ int s_cnt[1024], s_itm[1024];
+// single CTA: exclusive scans of count and of the per-bin item count, 1024 bins per round (warp shuffles, then the 32 warp
+// totals); also writes the bin of every work item
+__global__ void __launch_bounds__(1024) index_scan_kernel(IndexParams p) {
+  __shared__ int w_cnt[32], w_itm[32];
   __shared__ int carry_cnt, carry_itm;
   const int total = p.Hkv * p.NW * p.TB;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x == 0) { carry_cnt = 0; carry_itm = 0; }
   __syncthreads();
   for (int base = 0; base < total; base += 1024) {
     const int i = base + threadIdx.x;
     const int c = i < total ? p.count[i] : 0;
     const int it = (c + p.chunk - 1) / p.chunk;
-    s_cnt[threadIdx.x] = c;
-    s_itm[threadIdx.x] = it;
-    __syncthreads();
-    for (int off = 1; off < 1024; off <<= 1) {
-      int a = 0, bb = 0;
-      if (threadIdx.x >= off) { a = s_cnt[threadIdx.x - off]; bb = s_itm[threadIdx.x - off]; }
-      __syncthreads();
-      s_cnt[threadIdx.x] += a;
-      s_itm[threadIdx.x] += bb;
-      __syncthreads();
+    int vc = c, vi = it;  // inclusive scans within the warp
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int tc = __shfl_up_sync(0xffffffffu, vc, off), ti = __shfl_up_sync(0xffffffffu, vi, off);
+      if (lane >= off) { vc += tc; vi += ti; }
     }
+    if (lane == 31) { w_cnt[warp] = vc; w_itm[warp] = vi; }
+    __syncthreads();
+    if (warp == 0) {  // exclusive scan of the 32 warp totals
+      const int tc0 = w_cnt[lane], ti0 = w_itm[lane];
+      int sc = tc0, si = ti0;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int tc = __shfl_up_sync(0xffffffffu, sc, off), ti = __shfl_up_sync(0xffffffffu, si, off);
+        if (lane >= off) { sc += tc; si += ti; }
+      }
+      w_cnt[lane] = sc - tc0;
+      w_itm[lane] = si - ti0;
+    }
+    __syncthreads();
+    const int incl_c = carry_cnt + w_cnt[warp] + vc, incl_i = carry_itm + w_itm[warp] + vi;
     if (i < total) {
-      p.offsets[i] = carry_cnt + s_cnt[threadIdx.x] - c;
-      const int first = carry_itm + s_itm[threadIdx.x] - it;
+      p.offsets[i] = incl_c - c;
+      const int first = incl_i - it;
       p.item_base[i] = first;
       for (int k2 = 0; k2 < it; ++k2) p.item_bin[first + k2] = i;
     }
     __syncthreads();
-    if (threadIdx.x == 1023) { carry_cnt += s_cnt[1023]; carry_itm += s_itm[1023]; }
+    if (threadIdx.x == 1023) { carry_cnt = incl_c; carry_itm = incl_i; }
     __syncthreads();
   }
   if (threadIdx.x == 0) { p.offsets[total] = carry_cnt; p.item_base[total] = carry_itm; }
