@@ -202,7 +202,7 @@ def config_record():
 # scaled by tokens / 16384 for the workload at hand.
 NCU_DRAM_BYTES_16K = {
     "dense_fwd_tc": 0.271e9 + 226.9e6, "score_topk_tc": 0.275e9 + 6.3e6, "sparse_fwd": 0.306e9 + 241.0e6,
-    "sparse_dq": 0.851e9 + 259.3e6, "sparse_dkdv_tc": 1.623e9 + 116.8e6, "dense_dq_tc": 0.815e9 + 253.8e6,
+    "sparse_dq": 0.851e9 + 259.3e6, "sparse_dkdv_tc": 4.774e9 + 2.758e9, "dense_dq_tc": 0.815e9 + 253.8e6,
     "dense_dkdv_tc": 0.553e9 + 7.3e6,
 }
 
