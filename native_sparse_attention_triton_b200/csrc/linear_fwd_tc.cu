@@ -182,6 +182,7 @@ template <typename T, int D>
 static int launch_linear_fwd_tc(const void* x, const void* w, int batch, int max_y_len, int total_len, long long x_sn,
                                 long long x_sh, LinTcParams p, cudaStream_t stream) {
   if (D != kLinD) return kUnsupported;
+  if (batch > 65535) return kUnsupported;   // the batch is a grid dimension here; the caller falls back
   p.groups = total_len / p.stride;
   p.rem = total_len % p.stride;
   CUtensorMap tmXa, tmXb, tmW;

@@ -252,6 +252,7 @@ template <typename T, int D>
 static int launch_pool_bwd_stream(const void* x, int* slots_out, int batch, int total_len, int max_seqlen, int stride,
                                   long long x_sn, long long x_sh, PoolBwdStreamParams p, cudaStream_t stream) {
   p.hb = pb_heads(p.H);
+  if (batch > 65535) return kUnsupported;   // the batch is a grid dimension here; the caller falls back
   const long long chunk = (long long)stride * p.hb * D * 2;
   p.groups = kPbConsumers / (p.hb * (D / 8));
   p.slots = (int)std::min<long long>(kPbMaxBars / p.groups, kPbRingBytes / chunk / p.groups);

@@ -214,6 +214,7 @@ template <typename T, int D>
 static int launch_pool_fwd_stream(const void* x, int batch, int total_len, int total_y, int max_y_len, long long x_sn,
                                   long long x_sh, PoolStreamParams p, cudaStream_t stream) {
   p.hb = pool_stream_heads(p.H);
+  if (batch > 65535) return kUnsupported;   // the batch is a grid dimension here; the caller falls back
   const long long chunk = (long long)p.stride * p.hb * D * 2;
   p.groups = kPoolConsumers / (p.hb * (D / 8));
   p.slots = (int)std::min<long long>(kPoolMaxBars / p.groups, kPoolRingBytes / chunk / p.groups);
