@@ -175,8 +175,8 @@ def test_chain_backward_cfg_like(ops):
     (3, [120001, 15000], 16, 16),           # three heads (half-empty second head block); windows that do not overlap
     (4, [135000], 32, 8),                   # stride 8: four windows over every token
 ])
-@pytest.mark.parametrize("mode", ["weighted", "avg"])
-def test_pool_compress_backward_streaming_path(ops, H, seqlens, ks, st, mode):
+@pytest.mark.parametrize("mode,dtype", [("weighted", torch.bfloat16), ("avg", torch.bfloat16), ("weighted", torch.float16)])
+def test_pool_compress_backward_streaming_path(ops, H, seqlens, ks, st, mode, dtype):
     """Inputs of 131 072 tokens or more (head_dim 128, kernel <= 32) take the one-pass backward: dx written once, x and dy
     read once, dw from per-(CTA, group) partial rows added in a fixed order.  Against autograd through the oracle, run on the
     GPU in fp32; dw is a sum over ~10^7 products, compared relative to its own size."""
@@ -184,14 +184,14 @@ def test_pool_compress_backward_streaming_path(ops, H, seqlens, ks, st, mode):
     g = torch.Generator().manual_seed(300 + H + ks + st)
     N = sum(seqlens)
     cu = torch.tensor([0] + list(np.cumsum(seqlens)), dtype=torch.int32).cuda()
-    xb = torch.randn(N, H, d, generator=g).bfloat16()
-    wb = (torch.rand(H, ks, generator=g) / ks).bfloat16()
-    peb = (torch.randn(H, ks, d, generator=g) * 0.02).bfloat16()
+    xb = torch.randn(N, H, d, generator=g).to(dtype)
+    wb = (torch.rand(H, ks, generator=g) / ks).to(dtype)
+    peb = (torch.randn(H, ks, d, generator=g) * 0.02).to(dtype)
     x, pe = xb.cuda().requires_grad_(True), peb.cuda().requires_grad_(True)
     w = wb.cuda().requires_grad_(True) if mode == "weighted" else None
     fn = ops.weightedpool_compress if mode == "weighted" else ops.avgpool_compress
     y, _ = fn(x, w, cu, ks, st, pe)
-    dy = torch.randn(y.shape, generator=g).bfloat16().cuda()
+    dy = torch.randn(y.shape, generator=g).to(dtype).cuda()
     y.backward(dy)
     xr, per = xb.cuda().float().requires_grad_(True), peb.cuda().float().requires_grad_(True)
     wr = wb.cuda().float().requires_grad_(True) if mode == "weighted" else None
